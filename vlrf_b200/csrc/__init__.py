@@ -119,9 +119,9 @@ _SIGNATURES = {
                         _c_int, _c_int, _c_void_p],
     "vlrf_gemm_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void_p],
-    "vlrf_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_void_p, _c_int,
+    "vlrf_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_void_p, _c_int,
                            _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
-    "vlrf_latent_q_rows": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+    "vlrf_latent_q_rows": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "vlrf_attn_latent": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
@@ -138,11 +138,20 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p],
     "vlrf_moe_route": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_void_p],
+    "vlrf_moe_route_scored": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p,
+                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "vlrf_moe_plan": [_c_void_p, _c_void_p, _c_int, _c_void_p],
     "vlrf_moe_gather": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                         _c_void_p],
     "vlrf_moe_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                         _c_void_p],
+                         _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "vlrf_mingru_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                         _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
+    "vlrf_gate_mul_groups": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                             _c_int, _c_void_p],
+    "vlrf_rmsnorm_shift": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                           _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_add_row_vector": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,

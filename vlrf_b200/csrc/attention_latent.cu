@@ -15,9 +15,10 @@
 //   attn_latent     any mix of tokens; a warp per (token, head) walks the rows 0…position of its slot in chunks of
 //                   32 with an online softmax in float32.  The 32-bit path's attention and the fallback of the other.
 //
-// Rotation ("rotate half" pairing): of a vector's first `dims` entries, entry i is paired with entry i + dims/2;
-// the pair (u, v) at position p becomes (u cos a − v sin a, v cos a + u sin a), a = p · inv_freq[i]; entries beyond
-// `dims` pass unchanged.  inv_freq is a float32 table from the caller.
+// Rotation: of a vector's first `dims` entries, entry i is paired with entry i + dims/2 ("rotate half" pairing), or,
+// with `interleaved`, entry 2i with entry 2i + 1; the pair (u, v) at position p becomes (u cos a − v sin a,
+// v cos a + u sin a), a = p · inv_freq[i]; entries beyond `dims` pass unchanged.  inv_freq is a float32 table from the
+// caller.
 //
 // The cache of one layer is [block][BT][row_w] with row_w ≥ C + R; block_table as for the key/value cache.
 #include "common.cuh"
@@ -37,7 +38,7 @@ __device__ __forceinline__ void rotate_pair(float u, float v, float pos, float f
 template <typename ET>
 __global__ void __launch_bounds__(128)
 latent_append_kernel(const float* __restrict__ proj, int ld, int C, int R, const float* __restrict__ norm_w, float eps,
-                     const float* __restrict__ inv_freq, int rot_dims, ET* __restrict__ cache, int row_w,
+                     const float* __restrict__ inv_freq, int rot_dims, int interleaved, ET* __restrict__ cache, int row_w,
                      const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                      const int* __restrict__ tok_pos, int BT, int* __restrict__ dev_err) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
@@ -64,10 +65,11 @@ latent_append_kernel(const float* __restrict__ proj, int ld, int C, int R, const
     for (int i = threadIdx.x; i < C; i += 128) ElemIO<ET>::store(dst + i, src[i] * inv * norm_w[i]);
     const int half = rot_dims / 2;
     for (int i = threadIdx.x; i < half; i += 128) {
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
         float ou, ov;
-        rotate_pair(src[C + i], src[C + i + half], (float)pos, inv_freq[i], ou, ov);
-        ElemIO<ET>::store(dst + C + i, ou);
-        ElemIO<ET>::store(dst + C + i + half, ov);
+        rotate_pair(src[C + a], src[C + b], (float)pos, inv_freq[i], ou, ov);
+        ElemIO<ET>::store(dst + C + a, ou);
+        ElemIO<ET>::store(dst + C + b, ov);
     }
     for (int i = rot_dims + threadIdx.x; i < R; i += 128) ElemIO<ET>::store(dst + C + i, src[C + i]);
 }
@@ -75,7 +77,7 @@ latent_append_kernel(const float* __restrict__ proj, int ld, int C, int R, const
 template <typename ET>
 __global__ void __launch_bounds__(128)
 latent_q_rows_kernel(const float* __restrict__ q, int ld_q, int H, int dim, int R, const float* __restrict__ inv_freq,
-                     int rot_dims, const int* __restrict__ tok_pos, ET* __restrict__ qn, int ld_qn,
+                     int rot_dims, int interleaved, const int* __restrict__ tok_pos, ET* __restrict__ qn, int ld_qn,
                      ET* __restrict__ qp, int ld_qp, int C) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
@@ -90,11 +92,12 @@ latent_q_rows_kernel(const float* __restrict__ q, int ld_q, int H, int dim, int 
     for (int i = threadIdx.x; i < H * half; i += 128) {
         const int h = i / half, c = i - h * half;
         const float* s = src + h * per + dim;
+        const int a = interleaved ? 2 * c : c, b = interleaved ? 2 * c + 1 : c + half;
         float ou, ov;
-        rotate_pair(s[c], s[c + half], pos, inv_freq[c], ou, ov);
+        rotate_pair(s[a], s[b], pos, inv_freq[c], ou, ov);
         ET* d = qp + (size_t)t * ld_qp + (size_t)h * (C + R) + C;
-        ElemIO<ET>::store(d + c, ou);
-        ElemIO<ET>::store(d + c + half, ov);
+        ElemIO<ET>::store(d + a, ou);
+        ElemIO<ET>::store(d + b, ov);
     }
     const int rest = R - rot_dims;
     for (int i = threadIdx.x; i < H * rest; i += 128) {
@@ -199,7 +202,7 @@ attn_latent_kernel(const ET* __restrict__ qp, int ld_q, const ET* __restrict__ c
 }  // namespace
 
 extern "C" int vlrf_latent_append(const float* proj, int ld, int C, int R, const float* norm_w, float eps,
-                                  const float* inv_freq, int rot_dims, void* cache, int dtype, int row_w,
+                                  const float* inv_freq, int rot_dims, int interleaved, void* cache, int dtype, int row_w,
                                   const int* block_table, int max_blocks, const int* tok_slot, const int* tok_pos,
                                   int T, int BT, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && C > 0 && R >= 0 && ld >= C + R && row_w >= C + R && BT > 0 && max_blocks > 0, "latent_append: bad sizes");
@@ -208,14 +211,14 @@ extern "C" int vlrf_latent_append(const float* proj, int ld, int C, int R, const
     VLRF_REQUIRE(norm_w != nullptr && dev_err != nullptr, "latent_append: needs the norm's weight and the device error word");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        launch_chained(latent_append_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (float*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
+        launch_chained(latent_append_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, interleaved, (float*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
     else if (dtype == VLRF_BF16)
-        launch_chained(latent_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, (__nv_bfloat16*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
+        launch_chained(latent_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, proj, ld, C, R, norm_w, eps, inv_freq, rot_dims, interleaved, (__nv_bfloat16*)cache, row_w, block_table, max_blocks, tok_slot, tok_pos, BT, dev_err);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_append: unknown dtype %d", dtype);
     return vlrf_check_launch("latent_append");
 }
 
-extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims,
+extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims, int interleaved,
                                   const int* tok_pos, void* qn, int ld_qn, void* qp, int ld_qp, int C, int dtype, int T,
                                   cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && H > 0 && dim > 0 && R >= 0 && C >= 0, "latent_q_rows: bad sizes");
@@ -223,9 +226,9 @@ extern "C" int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int 
     VLRF_REQUIRE(rot_dims >= 0 && rot_dims <= R && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq != nullptr), "latent_q_rows: bad rotation");
     if (T == 0) return VLRF_OK;
     if (dtype == VLRF_F32)
-        launch_chained(latent_q_rows_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (float*)qn, ld_qn, (float*)qp, ld_qp, C);
+        launch_chained(latent_q_rows_kernel<float>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, interleaved, tok_pos, (float*)qn, ld_qn, (float*)qp, ld_qp, C);
     else if (dtype == VLRF_BF16)
-        launch_chained(latent_q_rows_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, tok_pos, (__nv_bfloat16*)qn, ld_qn, (__nv_bfloat16*)qp, ld_qp, C);
+        launch_chained(latent_q_rows_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)(0), stream, q, ld_q, H, dim, R, inv_freq, rot_dims, interleaved, tok_pos, (__nv_bfloat16*)qn, ld_qn, (__nv_bfloat16*)qp, ld_qp, C);
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "latent_q_rows: unknown dtype %d", dtype);
     return vlrf_check_launch("latent_q_rows");
 }

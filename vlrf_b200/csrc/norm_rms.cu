@@ -11,7 +11,18 @@
 //
 // cast_rows: float32 rows to the activation dtype (what a sublayer reads of the float32 residual stream).
 // gate_mul: out = act(a) · b element by element (act: x·sigmoid(x) or max(x, 0) for gated feed-forwards, sigmoid(x) for
-// gates on an attention's merged heads), float32 arithmetic.
+// gates on an attention's merged heads), float32 arithmetic.  gate_mul_groups: one column of a for every `per`
+// consecutive columns of b (a gate per head on the merged heads).
+//
+// rmsnorm_shift: the plain RMS norm of a token's residual row followed by a token shift: with n_t the normed row,
+// out_t = n_t + (n_(t−1) − n_t) · mu element by element, n_(t−1) being the normed row of the sequence's token before
+// (zeros ahead of the first).  The token before is the row above where the step brings it, else the sequence's kept
+// row: a float32 state [slot][2][d] holds the normed row of each sequence's last token twice, a step reading the copy
+// of the parity of the position it begins at and writing the copy of the parity of the position it ends at, so a step
+// of one token leaves what it read and may run twice.  The CTA of a sequence's first token of the step also norms the
+// sequence's last row of the step and keeps it, after it has read the kept row itself.
+//
+// add_row_vector: x[t] += v for every row (a vector that a model adds to the residual between layers).
 #include "common.cuh"
 
 namespace {
@@ -100,18 +111,113 @@ __global__ void gate_mul_f32x4_kernel(const float* a, int lda, const float* b, i
 }
 
 template <typename AT, typename BT, typename OT>
-__global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, int act) {
+__global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, int act, int per) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * cols) return;
     const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
-    const float g = ElemIO<AT>::load(a + (size_t)r * lda + c);
+    const float g = ElemIO<AT>::load(a + (size_t)r * lda + c / per);
     const float v = ElemIO<BT>::load(b + (size_t)r * ldb + c);
     const float f = gate_f(act, g);
     ElemIO<OT>::store(out + (size_t)r * ldo + c, f * v);
 }
+
+// the inverse root mean square of a float32 row, by the whole CTA (every thread gets it)
+__device__ __forceinline__ float row_inv_rms(const float* __restrict__ row, int d, float eps, float* part) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) { const float v = row[i]; s = fmaf(v, v, s); }
+    s = warp_sum(s);
+    __syncthreads();                                           // (part may still be read from the row before)
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < NORM_THREADS / 32; ++w) total += part[w];
+    return 1.f / sqrtf(total / (float)d + eps);
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_shift_kernel(const float* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ mu, float eps,
+                     float* state, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                     const int* __restrict__ seq_start, int n_seqs, int T, OT* __restrict__ out, int ld_out, int d) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    __shared__ float part[NORM_THREADS / 32];
+    const int t = blockIdx.x;
+    const int slot = tok_slot[t];
+    OT* o = out + (size_t)t * ld_out;
+    if (slot < 0) {                                            // padding row
+        for (int i = threadIdx.x; i < d; i += NORM_THREADS) ElemIO<OT>::store(o + i, 0.f);
+        return;
+    }
+    const int pos = tok_pos[t];
+    const bool row_above = t > 0 && tok_slot[t - 1] == slot;   // the token before came with this step
+    const float* xr = x + (size_t)t * ld_x;
+    const float inv = row_inv_rms(xr, d, eps, part);
+    float inv_prev = 0.f;
+    const float* prev = nullptr;                               // where the token before lies: a row of x, the state, or nowhere
+    if (row_above) {
+        prev = xr - ld_x;
+        inv_prev = row_inv_rms(prev, d, eps, part);
+    } else if (pos > 0) {
+        prev = state + ((size_t)slot * 2 + (pos & 1)) * d;
+    }
+    // the row that the sequence keeps: that of its last token of this step, normed by the CTA of its first
+    const float* last = nullptr;
+    float inv_last = 0.f;
+    float* keep = nullptr;
+    if (!row_above) {
+        int lo = 0, hi = n_seqs;                               // the sequence that begins at row t
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (seq_start[mid] < t) lo = mid + 1; else hi = mid; }
+        const int end = (lo < n_seqs && seq_start[lo] == t) ? seq_start[lo + 1] : t + 1;
+        const int n = min(end, T) - t;
+        last = xr + (size_t)(n - 1) * ld_x;
+        inv_last = n > 1 ? row_inv_rms(last, d, eps, part) : inv;
+        keep = state + ((size_t)slot * 2 + ((pos + n) & 1)) * d;
+    }
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+        const float g = w[i];
+        const float n_t = xr[i] * inv * g;
+        float n_prev = 0.f;
+        if (prev != nullptr) n_prev = row_above ? prev[i] * inv_prev * g : prev[i];
+        ElemIO<OT>::store(o + i, n_t + (n_prev - n_t) * mu[i]);
+        if (keep != nullptr) keep[i] = last[i] * inv_last * g;   // (after this thread's read of the kept row)
+    }
+}
+
+__global__ void add_row_vector_kernel(float* __restrict__ x, int ld, const float* __restrict__ v, int rows, int d) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * d) return;
+    const int r = (int)(i / d), c = (int)(i - (long long)r * d);
+    x[(size_t)r * ld + c] += v[c];
+}
 }  // namespace
+
+extern "C" int vlrf_rmsnorm_shift(const float* x, int ld_x, const float* w, const float* mu, float eps, float* state,
+                                  const int* tok_slot, const int* tok_pos, const int* seq_start, int n_seqs, int T, void* out,
+                                  int out_dtype, int ld_out, int d, cudaStream_t stream) {
+    VLRF_REQUIRE(T >= 0 && d > 0 && ld_x >= d && ld_out >= d && n_seqs >= 0, "rmsnorm_shift: bad sizes");
+    VLRF_REQUIRE(x && w && mu && state && tok_slot && tok_pos && seq_start && out, "rmsnorm_shift: a null pointer");
+    if (T == 0) return VLRF_OK;
+    if (out_dtype == VLRF_F32)
+        launch_chained(rmsnorm_shift_kernel<float>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (float*)out, ld_out, d);
+    else if (out_dtype == VLRF_BF16)
+        launch_chained(rmsnorm_shift_kernel<__nv_bfloat16>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (__nv_bfloat16*)out, ld_out, d);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "rmsnorm_shift: unknown output dtype %d", out_dtype);
+    return vlrf_check_launch("rmsnorm_shift");
+}
+
+extern "C" int vlrf_add_row_vector(float* x, int ld, const float* v, int rows, int d, cudaStream_t stream) {
+    VLRF_REQUIRE(rows >= 0 && d > 0 && ld >= d && x && v, "add_row_vector: bad arguments");
+    if (rows == 0) return VLRF_OK;
+    const long long n = (long long)rows * d;
+    launch_chained(add_row_vector_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, stream, x, ld, v, rows, d);
+    return vlrf_check_launch("add_row_vector");
+}
 
 extern "C" int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w, void* out, int out_dtype,
                                   int ld_out, int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16,
@@ -142,17 +248,31 @@ extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long lon
     return vlrf_check_launch("cast_rows");
 }
 
+static int gate_mul_any(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
+                        int out_dtype, int rows, int cols, int per, int act, cudaStream_t stream);
+
 extern "C" int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
                              int out_dtype, int rows, int cols, int act, cudaStream_t stream) {
-    VLRF_REQUIRE(rows >= 0 && cols > 0 && lda >= cols && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
+    return gate_mul_any(a, lda, a_dtype, b, ldb, b_dtype, out, ldo, out_dtype, rows, cols, 1, act, stream);
+}
+
+extern "C" int vlrf_gate_mul_groups(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
+                                    int out_dtype, int rows, int cols, int per, int act, cudaStream_t stream) {
+    VLRF_REQUIRE(per > 0 && cols % per == 0, "gate_mul_groups: %d columns are no whole groups of %d", cols, per);
+    return gate_mul_any(a, lda, a_dtype, b, ldb, b_dtype, out, ldo, out_dtype, rows, cols, per, act, stream);
+}
+
+static int gate_mul_any(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
+                        int out_dtype, int rows, int cols, int per, int act, cudaStream_t stream) {
+    VLRF_REQUIRE(rows >= 0 && cols > 0 && per > 0 && lda >= cols / per && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
     VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID || act == VLRF_ACT_RELU, "gate_mul: the gate is x*sigmoid(x), sigmoid(x) or max(x, 0), not %d", act);
     if (rows == 0) return VLRF_OK;
     const long long n = (long long)rows * cols;
     const dim3 blocks((unsigned)((n + 255) / 256));
-    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+    const bool aligned = per == 1 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                          cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
     typedef __nv_bfloat16 bf;
-#define GO(AT, BT, OT) launch_chained(gate_mul_kernel<AT, BT, OT>, blocks, dim3(256), (size_t)0, stream, (const AT*)a, lda, (const BT*)b, ldb, (OT*)out, ldo, rows, cols, act)
+#define GO(AT, BT, OT) launch_chained(gate_mul_kernel<AT, BT, OT>, blocks, dim3(256), (size_t)0, stream, (const AT*)a, lda, (const BT*)b, ldb, (OT*)out, ldo, rows, cols, act, per)
     if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && aligned)
         launch_chained(gate_mul_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), (size_t)0, stream, (const bf*)a, lda, (const bf*)b, ldb,
                        (bf*)out, ldo, rows, cols / 8, act);

@@ -574,6 +574,40 @@ def group_rmsnorm(y, weight, eps: float, groups: int, out, rows=None, accumulate
          float(eps), 1 if accumulate else 0, _ptr(also), _stream())
 
 
+def rmsnorm_shift(x, weight, mu, eps: float, state, ctx, out) -> None:
+    """The plain RMS norm of the step's float32 residual rows followed by a token shift (see the kernel library's
+    header): out[t] = n_t + (n_before − n_t) · mu.  state: float32 [slots, 2, d], the normed row of every sequence's last
+    token, read and written by the parity of the positions."""
+    _rows(x, "x", torch.float32); _dev(weight, "weight", torch.float32); _dev(mu, "mu", torch.float32)
+    _dev(state, "state", torch.float32); _rows(out, "out")
+    d, T = weight.shape[0], ctx.n_tokens
+    if x.shape[1] < d or mu.shape[0] != d or out.shape[1] < d or min(x.shape[0], out.shape[0]) < T or state.dim() != 3 \
+            or tuple(state.shape[1:]) != (2, d) or not state.is_contiguous():
+        raise KernelError("rmsnorm_shift: sizes do not match")
+    call("vlrf_rmsnorm_shift", _ptr(x), x.stride(0), _ptr(weight), _ptr(mu), float(eps), _ptr(state), _ptr(ctx.tok_slot),
+         _ptr(ctx.tok_pos), _ptr(ctx.seq_start), ctx.n_seqs, T, _ptr(out), dtype_code(out.dtype), out.stride(0), d, _stream())
+
+
+def add_row_vector(x, v, n_rows: int) -> None:
+    """x[r] += v for the first n_rows float32 rows."""
+    _rows(x, "x", torch.float32); _dev(v, "v", torch.float32)
+    if x.shape[1] < v.shape[0] or x.shape[0] < n_rows:
+        raise KernelError("add_row_vector: sizes do not match")
+    call("vlrf_add_row_vector", _ptr(x), x.stride(0), _ptr(v), n_rows, v.shape[0], _stream())
+
+
+def mingru_scan(proj, z_off: int, u_off: int, g_off: int, width: int, state, ctx, out) -> None:
+    """The element-wise gated recurrence over the step's tokens (see the kernel library's header): proj float32 with the
+    gate logits, candidate inputs and output gate logits at three column offsets; state float32 [slots, 2, width]."""
+    _rows(proj, "proj", torch.float32); _dev(state, "state", torch.float32); _rows(out, "out")
+    T = ctx.n_tokens
+    if state.dim() != 3 or tuple(state.shape[1:]) != (2, width) or not state.is_contiguous() or out.shape[1] < width \
+            or min(proj.shape[0], out.shape[0]) < T or proj.shape[1] < width + max(z_off, u_off, g_off):
+        raise KernelError("mingru_scan: sizes do not match")
+    call("vlrf_mingru_scan", _ptr(proj), proj.stride(0), z_off, u_off, g_off, width, _ptr(state), _ptr(ctx.seq_slot),
+         _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), ctx.n_seqs, ctx.max_new, _ptr(out), dtype_code(out.dtype), out.stride(0), _stream())
+
+
 def cast_rows(x, out, n_rows: int) -> None:
     """The first n_rows float32 rows of x in out's dtype."""
     _dev(x, "x", torch.float32); _dev(out, "out")
@@ -582,13 +616,20 @@ def cast_rows(x, out, n_rows: int) -> None:
     call("vlrf_cast_rows", _ptr(x), _ptr(out), dtype_code(out.dtype), n_rows * x.shape[1], _stream())
 
 
-def gate_mul(a, b, out, gate: str, n_rows: int, cols: int) -> None:
+def gate_mul(a, b, out, gate: str, n_rows: int, cols: int, per: int = 1) -> None:
     """out[r, :cols] = gate(a[r, :cols]) · b[r, :cols]; gate "silu", "sigmoid" or "relu".  a, b and out may be column ranges
-    of wider rows, and out may be a or b.  a and b may be float32 where out is bfloat16 (see the kernel library's header)."""
+    of wider rows, and out may be a or b.  a and b may be float32 where out is bfloat16 (see the kernel library's header).
+    per > 1: one column of a for every `per` consecutive columns of b (a gate per head on merged heads)."""
     for name, t in (("a", a), ("b", b), ("out", out)):
         _rows(t, name)
-        if t.shape[0] < n_rows or t.shape[1] < cols:
+        if t.shape[0] < n_rows or t.shape[1] < (cols // per if name == "a" else cols):
             raise KernelError(f"gate_mul: {name} does not match")
+    if per != 1:
+        if per < 1 or cols % per != 0:
+            raise KernelError(f"gate_mul: {cols} columns are no whole groups of {per}")
+        call("vlrf_gate_mul_groups", _ptr(a), a.stride(0), dtype_code(a.dtype), _ptr(b), b.stride(0), dtype_code(b.dtype), _ptr(out),
+             out.stride(0), dtype_code(out.dtype), n_rows, cols, int(per), GATE[gate], _stream())
+        return
     call("vlrf_gate_mul", _ptr(a), a.stride(0), dtype_code(a.dtype), _ptr(b), b.stride(0), dtype_code(b.dtype), _ptr(out),
          out.stride(0), dtype_code(out.dtype), n_rows, cols, GATE[gate], _stream())
 
@@ -638,7 +679,7 @@ def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
 # ---- attention over a cache of latents --------------------------------------------------------------------------------
 
 def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_dims: int, cache, block_table, tok_slot,
-                  tok_pos, n_tokens: int, dev_err) -> None:
+                  tok_pos, n_tokens: int, dev_err, interleaved: bool = False) -> None:
     """Each token's row [RMSnorm(proj[:C]) · weight | rotate(proj[C:C+R])] into the paged cache [block, BT, row]."""
     _rows(proj, "proj", torch.float32); _dev(norm_weight, "norm_weight", torch.float32); _dev(cache, "cache")
     _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
@@ -650,11 +691,12 @@ def latent_append(proj, C: int, R: int, norm_weight, eps: float, inv_freq, rot_d
     if proj.shape[1] < C + R or cache.shape[2] < C + R or norm_weight.shape[0] != C or proj.shape[0] < n_tokens:
         raise KernelError("latent_append: sizes do not match")
     call("vlrf_latent_append", _ptr(proj), proj.stride(0), C, R, _ptr(norm_weight), float(eps), _ptr(inv_freq), int(rot_dims),
-         _ptr(cache), dtype_code(cache.dtype), cache.shape[2], _ptr(block_table), block_table.shape[1], _ptr(tok_slot),
+         1 if interleaved else 0, _ptr(cache), dtype_code(cache.dtype), cache.shape[2], _ptr(block_table), block_table.shape[1], _ptr(tok_slot),
          _ptr(tok_pos), n_tokens, cache.shape[1], _ptr(dev_err), _stream())
 
 
-def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, tok_pos, qn, qp, C: int, n_tokens: int) -> None:
+def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, tok_pos, qn, qp, C: int, n_tokens: int,
+                  interleaved: bool = False) -> None:
     """q float32 [T, H·(dim + R)] → qn [T, H·dim] (unrotated parts) and the last R columns of each head's C + R columns
     of qp (rotated parts, rotated by position)."""
     _rows(q, "q", torch.float32); _dev(qn, "qn"); _dev(qp, "qp", qn.dtype); _dev(tok_pos, "tok_pos", torch.int32)
@@ -662,7 +704,7 @@ def latent_q_rows(q, n_heads: int, dim: int, R: int, inv_freq, rot_dims: int, to
         _dev(inv_freq, "inv_freq", torch.float32)
     if q.shape[1] != n_heads * (dim + R) or qn.shape[1] != n_heads * dim or qp.shape[1] != n_heads * (C + R):
         raise KernelError("latent_q_rows: sizes do not match")
-    call("vlrf_latent_q_rows", _ptr(q), q.stride(0), n_heads, dim, R, _ptr(inv_freq), int(rot_dims), _ptr(tok_pos), _ptr(qn),
+    call("vlrf_latent_q_rows", _ptr(q), q.stride(0), n_heads, dim, R, _ptr(inv_freq), int(rot_dims), 1 if interleaved else 0, _ptr(tok_pos), _ptr(qn),
          qn.shape[1], _ptr(qp), qp.shape[1], C, dtype_code(qn.dtype), n_tokens, _stream())
 
 
@@ -779,6 +821,10 @@ def attention_latent(qp, cache, C: int, R: int, block_table, tok_slot, tok_pos, 
 
 # ---- routed experts --------------------------------------------------------------------------------------------------
 
+#: the most router outputs that the routing kernels take
+MOE_MAX_OUTPUTS = 512
+
+
 def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts, rank, gate, counts, n_tokens: int) -> None:
     """From float32 router logits z [T, ≥ E (+1)]: ids, wts, rank [T, top], gate [T] (see the kernel library's header)."""
     _rows(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
@@ -793,6 +839,22 @@ def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts
         raise KernelError("moe_route: the logits' rows are too short")
     call("vlrf_moe_route", _ptr(z), z.stride(0), n_experts, top, 1 if shared_gate else 0, _ptr(tok_slot), _ptr(ids), _ptr(wts),
          _ptr(rank), _ptr(gate), _ptr(counts), n_tokens, _stream())
+
+
+def moe_route_scored(z, n_outputs: int, top: int, groups: int, keep: int, n_identity: int, scale: float, correction, tok_slot,
+                     ids, wts, rank, counts, n_tokens: int) -> None:
+    """From float32 router logits z [T, ≥ n_outputs]: softmax over all outputs, the choice by score + correction inside the
+    `keep` best of `groups` groups, weights score · scale; the last n_identity outputs get id −2 and no rank (see the
+    kernel library's header)."""
+    _rows(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
+    _dev(rank, "rank", torch.int32); _dev(counts, "counts", torch.int32); _dev(correction, "correction", torch.float32)
+    if tok_slot is not None:
+        _dev(tok_slot, "tok_slot", torch.int32)
+    if z.shape[0] < n_tokens or z.shape[1] < n_outputs or ids.numel() < n_tokens * top or correction.numel() < n_outputs \
+            or counts.numel() < max(n_outputs - n_identity, 1):
+        raise KernelError("moe_route_scored: sizes do not match")
+    call("vlrf_moe_route_scored", _ptr(z), z.stride(0), n_outputs, top, int(groups), int(keep), int(n_identity), float(scale),
+         _ptr(correction), _ptr(tok_slot), _ptr(ids), _ptr(wts), _ptr(rank), _ptr(counts), n_tokens, _stream())
 
 
 def moe_plan(counts, offsets, n_experts: int) -> None:
@@ -810,15 +872,22 @@ def moe_gather(h, ids, rank, offsets, sorted_rows, row_of, n_tokens: int, top: i
          _ptr(row_of), n_tokens, top, _stream())
 
 
-def moe_combine(expert_out, row_of, wts, top: int, shared_out, gate, y, n_tokens: int, residual=None) -> None:
-    """y[t] = Σ_j wts[t, j] · expert_out[row_of[t, j]] (+ gate[t] · shared_out[t]) (+ residual[t]), float32."""
+def moe_combine(expert_out, row_of, wts, top: int, shared_out, gate, y, n_tokens: int, residual=None, ids=None, h=None) -> None:
+    """y[t] = Σ_j wts[t, j] · expert_out[row_of[t, j]] (+ gate[t] · shared_out[t]) (+ residual[t]), float32.  With `ids` and
+    the experts' input rows `h`: a pair whose id is −2 (an expert that returns its input) adds wts[t, j] · h[t]."""
     _dev(expert_out, "expert_out", torch.float32); _dev(y, "y", torch.float32)
+    if (ids is None) != (h is None):
+        raise KernelError("moe_combine: experts that return their input need ids and the input rows")
+    if h is not None:
+        _dev(ids, "ids", torch.int32); _dev(h, "h")
+        if h.shape[1] != y.shape[1] or h.shape[0] < n_tokens or not h.is_contiguous():
+            raise KernelError("moe_combine: the input rows do not match")
     if shared_out is not None:
         _dev(shared_out, "shared_out", torch.float32)
     if y.shape[1] != expert_out.shape[1] or y.shape[0] < n_tokens:
         raise KernelError("moe_combine: sizes do not match")
     call("vlrf_moe_combine", _ptr(expert_out), expert_out.shape[1], _ptr(row_of), _ptr(wts), top, _ptr(shared_out), _ptr(gate),
-         _ptr(residual), _ptr(y), n_tokens, _stream())
+         _ptr(residual), _ptr(y), n_tokens, _ptr(ids), _ptr(h), dtype_code(h.dtype) if h is not None else 0, _stream())
 
 
 # ---- a residual in several streams -------------------------------------------------------------------------------------

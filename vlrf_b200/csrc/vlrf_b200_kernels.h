@@ -190,6 +190,21 @@ int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaSt
 // a or b).  Dtypes (a, b → out): all bfloat16; all float32; float32, bfloat16 → bfloat16; float32, float32 → bfloat16.
 int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
                   int rows, int cols, int act, cudaStream_t stream);
+// The same with one column of a for every `per` consecutive columns of b: out[r][c] = act(a[r][c / per]) · b[r][c] (a gate
+// per head on the merged heads); cols a multiple of per.
+int vlrf_gate_mul_groups(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
+                         int rows, int cols, int per, int act, cudaStream_t stream);
+// Plain RMS norm and token shift of the step's residual rows: with n_t = x[t] / sqrt(mean(x[t]²) + eps) · w,
+// out[t] = n_t + (n_before − n_t) · mu, n_before being the normed row of the sequence's token before: the row above
+// where tok_slot[t−1] = tok_slot[t], zeros at position 0, else the sequence's kept row.  state: float32 [slots][2][d];
+// a step reads copy (position at its start) mod 2 and writes the normed row of the sequence's last token of the step
+// into copy (position behind it) mod 2.  seq_start [n_seqs + 1]: the first row of every sequence of the step.  Rows
+// with slot −1 get zeros.  x float32 [T][ld_x]; out of out_dtype [T][ld_out]; w, mu float32 [d].
+int vlrf_rmsnorm_shift(const float* x, int ld_x, const float* w, const float* mu, float eps, float* state, const int* tok_slot,
+                       const int* tok_pos, const int* seq_start, int n_seqs, int T, void* out, int out_dtype, int ld_out, int d,
+                       cudaStream_t stream);
+// x[r][c] += v[c] for r < rows, c < d; float32.
+int vlrf_add_row_vector(float* x, int ld, const float* v, int rows, int d, cudaStream_t stream);
 
 // ---- a residual in several streams (streams.cu) -------------------------------------------------------------------------
 // x[t][s] = table[tokens[t]] · scale for every stream s < S: float32 [T][S][d] from a table [V][d] of w_dtype.
@@ -265,15 +280,16 @@ int vlrf_gemm_grouped(const void* X, const void* W, void* Y, const int* offsets,
 // ---- attention over a cache of latents (attention_latent.cu) -----------------------------------------------------------
 // The cache of one layer is [n_blocks][BT][row_w] of `dtype`: per token a row [c | r], the normed latent (C numbers)
 // and a rotated key part shared by all heads (R numbers, R may be 0).  Rotation: of the first rot_dims entries, entry
-// i pairs with entry i + rot_dims/2; angle = position · inv_freq[i] (float32 table of rot_dims/2 entries).
+// i pairs with entry i + rot_dims/2 (interleaved != 0: entry 2i with entry 2i + 1); angle = position · inv_freq[i]
+// (float32 table of rot_dims/2 entries).
 // proj: float32 [T][ld], columns 0…C−1 the latent before its RMS norm (weight norm_w, eps), C…C+R−1 the key part
 // before its rotation; the token's row is written at (tok_slot, tok_pos).
 int vlrf_latent_append(const float* proj, int ld, int C, int R, const float* norm_w, float eps, const float* inv_freq,
-                       int rot_dims, void* cache, int dtype, int row_w, const int* block_table, int max_blocks,
+                       int rot_dims, int interleaved, void* cache, int dtype, int row_w, const int* block_table, int max_blocks,
                        const int* tok_slot, const int* tok_pos, int T, int BT, int* dev_err, cudaStream_t stream);
 // q: float32 [T][ld_q], per head [dim | R].  qn [T][ld_qn]: the heads' first dim columns, compact; qp [T][ld_qp]:
 // per head a row of C + R columns whose last R receive the rotated part (the first C are left for vlrf_gemm_heads).
-int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims, const int* tok_pos,
+int vlrf_latent_q_rows(const float* q, int ld_q, int H, int dim, int R, const float* inv_freq, int rot_dims, int interleaved, const int* tok_pos,
                        void* qn, int ld_qn, void* qp, int ld_qp, int C, int dtype, int T, cudaStream_t stream);
 // qp [T][ld_q]: per head C + R numbers (the query in latent space, then its rotated part).  out [T][ld_out]: per head
 // the C numbers Σ_j p_j c_j with p = softmax_j((qp_h · row_j) · scale) over the visible rows j ≤ position (and, with
@@ -314,15 +330,34 @@ int vlrf_attn_latent_mma(const void* qp, int ld_q, const void* cache, int row_w,
 // chosen logits, the pair's rank among its expert's rows; gate [T] = sigmoid(z[t][E]); counts int32 [E], zero before.
 int vlrf_moe_route(const float* z, int ld_z, int E, int top, int shared_gate, const int* tok_slot, int* ids, float* wts,
                    int* rank, float* gate, int* counts, int T, cudaStream_t stream);
+// Routing by scores: s = softmax(z) over all E router outputs; a token chooses by s + correction (float32 [E]) among
+// the outputs of the `keep` best of `groups` equal groups of neighbours (a group's score: its largest s + correction;
+// ties to the lower index everywhere) and weighs the chosen by s · scale.  The last n_identity outputs stand for
+// experts without matrices that return their input: such a pair gets ids −2 and no row (padding rows: −1); counts
+// int32 [E − n_identity], zero before.  top ≤ keep · E / groups.
+int vlrf_moe_route_scored(const float* z, int ld_z, int E, int top, int groups, int keep, int n_identity, float scale,
+                          const float* correction, const int* tok_slot, int* ids, float* wts, int* rank, int* counts, int T,
+                          cudaStream_t stream);
 // offsets[e] = Σ counts[< e], E + 1 entries; counts are left zero.
 int vlrf_moe_plan(int* counts, int* offsets, int E, cudaStream_t stream);
 // sorted[offsets[ids[p]] + rank[p]] = h[p / top] for every pair p < T·top with an expert; row_of[p] = that row or −1.
 int vlrf_moe_gather(const void* h, int dtype, int width, const int* ids, const int* rank, const int* offsets, void* sorted,
                     int* row_of, int T, int top, cudaStream_t stream);
 // y[t] = Σ_j wts[t][j] · expert_out[row_of[t][j]] (+ (gate ? gate[t] : 1) · shared_out[t] if shared_out) (+ residual[t]
-// if residual, which may be y), float32.
+// if residual, which may be y), float32.  With ids and h (the experts' input rows, of h_dtype [T][width]): a pair
+// whose ids entry is −2 adds wts · h[t] (an expert that returns its input).
 int vlrf_moe_combine(const float* expert_out, int width, const int* row_of, const float* wts, int top,
                      const float* shared_out, const float* gate, const float* residual, float* y, int T,
+                     const int* ids, const void* h, int h_dtype, cudaStream_t stream);
+
+// ---- a gated recurrence element by element (mingru.cu) ---------------------------------------------------------------
+// proj: float32 [T][ld] with, per token, W gate logits at column z_off, W candidate inputs at u_off and W output gate
+// logits at g_off.  z = sigmoid(·), c = u + 1/2 where u ≥ 0 and sigmoid(u) below, S ← (1 − z) · S + z · c element by
+// element along each sequence, out[t] = S_t · g · sigmoid(g) in out_dtype [T][ld_out].  state: float32 [slots][2][W],
+// read at copy (seq_pos0 mod 2) unless seq_pos0 = 0 (zeros), written at copy ((seq_pos0 + tokens) mod 2).  Sequence i
+// brings the rows seq_start[i] … seq_start[i+1]−1 for slot seq_slot[i] (−1: padding, skipped); max_new the longest run.
+int vlrf_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, int W, float* state, const int* seq_slot,
+                     const int* seq_start, const int* seq_pos0, int n_seqs, int max_new, void* out, int out_dtype, int ld_out,
                      cudaStream_t stream);
 
 // ---- sampling (sampling.cu) ----------------------------------------------------------------------------------------

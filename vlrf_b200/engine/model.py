@@ -11,6 +11,7 @@ import dataclasses
 
 import torch
 
+from ..csrc import ops
 from ..parts.context import StepContext
 
 
@@ -18,6 +19,9 @@ from ..parts.context import StepContext
 class LayerCall:
     layer: int                    # index into DecoderModel.layers
     reads_cache_of: int | None = None   # index of an earlier call in the schedule, or None: own cache
+    #: a float32 vector [residual width] that is added to every residual row before the layer runs (say, a vector of
+    #: its own for each pass of a range of layers that runs several times), or None
+    add_before: object = dataclasses.field(default=None, compare=False)
 
 
 @dataclasses.dataclass
@@ -117,6 +121,8 @@ class DecoderModel:
         x = program.scratch("residual", rows, self.width, torch.float32)
         self.embedding.emit_decode(program, x)
         for i, call in enumerate(self.schedule):
+            if call.add_before is not None:
+                raise NotFusable("a vector added between layers is not an operation of the decode program")
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
             self.layers[call.layer].emit_decode(program, x, view, writes_cache=call.reads_cache_of is None)
@@ -139,6 +145,11 @@ class DecoderModel:
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
             ctx.next_block = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            if call.add_before is not None:
+                ops.add_row_vector(x, call.add_before, ctx.n_tokens)
+                ctx.ws.row_stats.forget()
+                ctx.ws.input_cast = None
+                ctx.ws.normed_ready = None             # (a block ahead may have read the rows for this one already)
             self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
             if not getattr(self.layers[call.layer], "leaves_row_stats", False):
                 ctx.ws.row_stats.forget()              # a block of another kind that does not vouch for them

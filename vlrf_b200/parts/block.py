@@ -10,13 +10,33 @@ from .registry import register_part
 @register_part("block", "pre_norm")
 class PreNormBlock:
     """x += mixer(norm1(x)); x += ffn(norm2(x)) (reference: include/model/transformer_block.hpp:149-159).
-    The residual stream x stays float32; the normed rows are in the activation dtype."""
+    The residual stream x stays float32; the normed rows are in the activation dtype.
+
+    A first norm that keeps something per sequence (one with a `cache_need` of its own, such as a norm with a token
+    shift) is given the step and its state; what it keeps is the last entry of the block's need, behind the mixer's."""
 
     def __init__(self, norm1, mixer, norm2, feed_forward):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self._norm_keeps = hasattr(norm1, "cache_need")
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        need = self.mixer.cache_need()
+        if not self._norm_keeps:
+            return need
+        own = self.norm1.cache_need()
+        if need is None:
+            return (own,)
+        return (*need, own) if isinstance(need, tuple) else (need, own)
+
+    def _views(self, view):
+        """(the mixer's view, the first norm's state) of a block whose first norm keeps something."""
+        from ..cache import CacheView
+        parts = view.parts
+        if len(parts) == 1:
+            return None, parts[0].state
+        if len(parts) == 2:
+            return parts[0], parts[1].state
+        return CacheView(tuple(p.need for p in parts[:-1]), parts=parts[:-1]), parts[-1].state
 
     @property
     def leaves_row_stats(self) -> bool:
@@ -27,6 +47,8 @@ class PreNormBlock:
         """This block's decode step as operations of a decode program: possible when the mixer and the
         feed-forward can state theirs (they get the norm to fuse, as in `forward`)."""
         from .program import NotFusable
+        if self._norm_keeps:
+            raise NotFusable("a norm that keeps a state is not an operation of the decode program")
         for part in (self.mixer, self.feed_forward):
             if not hasattr(part, "emit_decode"):
                 raise NotFusable(f"{type(part).__name__} has no emit_decode")
@@ -34,7 +56,13 @@ class PreNormBlock:
         self.feed_forward.emit_decode(program, x, self.norm2)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
-        if getattr(self.mixer, "fuses_norm", False):
+        if self._norm_keeps:
+            if not writes_cache:
+                raise ValueError("PreNormBlock: a layer whose norm keeps a state cannot run on another layer's cache")
+            mixer_view, kept = self._views(view)
+            h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
+            self.mixer.forward(self.norm1(x, h, ctx=ctx, state=kept), x, ctx, mixer_view, writes_cache)
+        elif getattr(self.mixer, "fuses_norm", False):
             self.mixer.forward(None, x, ctx, view, writes_cache, norm=self.norm1)
         else:
             h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)

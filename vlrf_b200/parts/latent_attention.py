@@ -11,8 +11,8 @@ head), every head attends the rows themselves, and the head's result is carried 
 head).  That is the same arithmetic with the sums taken in another order.
 
 What is a parameter: how queries are made (directly, h·W_qᵀ, or through a latent of their own, RMSnorm(h·W_dqᵀ)·W_uqᵀ);
-the rotated part and its rotation (a position part that acts on q/k, or none); a sigmoid gate on the merged heads
-(W_g, from the same input); whether the layer owns a cache row (W_dkv and its norm) or reads another layer's, as the
+the rotated part and its rotation (a position part that acts on q/k, with the pairing it names, or none); a sigmoid
+gate on the merged heads (W_g, from the same input: a row per merged column, or a row per head); whether the layer owns a cache row (W_dkv and its norm) or reads another layer's, as the
 model's schedule says (`writes_cache=False`: it then has no W_dkv and uses the rows as they lie in the cache).
 Norms, rotation angles, scores and softmax are float32; products take operands in the activation dtype.
 """
@@ -48,8 +48,8 @@ class LatentAttention:
             raise ValueError("latent attention: the output projection does not take the merged heads")
         if w_dkv is not None and (w_dkv.shape[0] != C + R or dkv_norm is None or dkv_norm.shape[0] != C):
             raise ValueError(f"latent attention: W_dkv has kv_rank + rot_dim = {C + R} rows and a norm weight of {C}")
-        if w_gate is not None and w_gate.shape[0] != H * vdim:
-            raise ValueError("latent attention: the gate has one row per merged column")
+        if w_gate is not None and w_gate.shape[0] not in (H * vdim, H):
+            raise ValueError("latent attention: the gate has one row per merged column, or one per head")
         if R > 0:
             if rotary is None or getattr(rotary, "where", None) != "qk" or rotary.dims > R:
                 raise ValueError("latent attention: a rotated part needs a rotation of at most its own size")
@@ -60,6 +60,8 @@ class LatentAttention:
         self.w_q, self.w_dq, self.dq_norm, self.w_uq = w_q, w_dq, dq_norm, w_uq
         self.w_dkv, self.dkv_norm, self.w_gate, self.w_out = w_dkv, dkv_norm, w_gate, w_out
         self.rotary = rotary if R > 0 else None
+        # merged columns that share one gate logit: 1 (a gate per column) or vdim (a gate per head)
+        self.gate_per = 1 if w_gate is None or w_gate.shape[0] == H * vdim else int(vdim)
         # Uk per head, transposed once: [H, kv_rank, dim], the operand that carries a head's query into latent space;
         # Uv per head as it is stored: [H, vdim, kv_rank]
         self.w_uk_t = w_uk.view(H, dim, C).transpose(1, 2).contiguous()
@@ -96,11 +98,13 @@ class LatentAttention:
         D = C + R
         inv_freq = self.rotary.inv_freq if self.rotary is not None else None
         rot_dims = self.rotary.dims if self.rotary is not None else 0
+        pairs = bool(getattr(self.rotary, "interleaved", False))
         if writes_cache and self.w_dkv is None:
             raise ValueError("latent attention: a layer without W_dkv reads another layer's cache and cannot write one")
         # few rows (a decode step): the gate's logits ride in the same product, as float32; many rows: they are a
         # product of their own in the activation dtype, half the bytes
-        proj, gate_apart = None, self.w_gate is not None and T > ops.SKINNY_MAX_ROWS
+        # (a gate per head is a handful of columns and always rides along)
+        proj, gate_apart = None, self.w_gate is not None and T > ops.SKINNY_MAX_ROWS and self.gate_per == 1
         if self.w_in is not None:
             n_in = self._cols["gate"][0] if gate_apart else self.w_in.shape[0]
             if n_in > 0:
@@ -113,7 +117,7 @@ class LatentAttention:
 
         if writes_cache:
             ops.latent_append(cols("kv"), C, R, self.dkv_norm, self.eps, inv_freq, rot_dims, view.rows, view.block_table,
-                              ctx.tok_slot, ctx.tok_pos, T, ctx.dev_err)
+                              ctx.tok_slot, ctx.tok_pos, T, ctx.dev_err, interleaved=pairs)
         # A prompt step whose sequences all begin at position 0 holds every key and value it needs itself: they are
         # formed (two products of the step's latents) and attended as plain rows, which takes (dim + R) + vdim
         # multiplications per query, key and head instead of the latent-space form's (C + R) + C.  Every other step
@@ -132,11 +136,11 @@ class LatentAttention:
             else:
                 q32 = ws.get("latent_q32", T, H * (dim + R), torch.float32)
                 ops.linear(cq, self.w_uq, None, q32)
-                ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T)
+                ops.latent_q_rows(q32, H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T, interleaved=pairs)
         elif R == 0:
             ops.linear(h, self.w_q, None, qn)
         else:
-            ops.latent_q_rows(cols("q"), H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T)
+            ops.latent_q_rows(cols("q"), H, dim, R, inv_freq, rot_dims, ctx.tok_pos, qn, qp, q_c, T, interleaved=pairs)
         merged = ws.get("attn_out", T, H * vdim, act)
         if as_rows:
             rows_c = ws.get("latent_step_c", T, C, act)
@@ -156,5 +160,5 @@ class LatentAttention:
             ops.linear(h, self.w_gate, None, g)
             ops.gate_mul(g, merged, merged, "sigmoid", T, H * vdim)
         elif self.w_gate is not None:
-            ops.gate_mul(cols("gate"), merged, merged, "sigmoid", T, H * vdim)
+            ops.gate_mul(cols("gate"), merged, merged, "sigmoid", T, H * vdim, per=self.gate_per)
         ops.linear(merged, self.w_out, None, x, residual=x if accumulate else None)

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from ..cache import StateNeed
 from ..csrc import ops
 from .registry import register_part
 
@@ -62,4 +63,30 @@ class StreamSumRMSNorm:
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int | None = None) -> torch.Tensor:
         ops.streams_read_norm(x, self.streams, self.coefficients, self.weight, self.eps, out, rows, n_rows)
+        return out
+
+
+@register_part("norm", "rmsnorm_shift")
+class ShiftedRMSNorm:
+    """The plain RMS norm followed by a token shift: with n_t = x_t / sqrt(mean(x_t²) + eps) · weight,
+
+        y_t = n_t + (n_(t−1) − n_t) · mu      (element by element; n_(−1) = 0),
+
+    n_(t−1) being the normed row of the sequence's token before, as it was before any shift.  A step that does not bring
+    that token finds its normed row in the sequence's state, so this norm keeps something per sequence and says so
+    (`cache_need`): a float32 row held twice, read and written by the parity of the positions, so that a step of one
+    token may run twice.  The block that owns the norm hands it the step and its state.  The norm, the difference and
+    the sum are float32; y is rounded once to the activation dtype."""
+
+    def __init__(self, weight: torch.Tensor, mu: torch.Tensor, eps: float):
+        if weight.dim() != 1 or mu.shape != weight.shape:
+            raise ValueError("ShiftedRMSNorm: the weight and the shift's coefficients are vectors of one length")
+        self.weight, self.mu, self.eps = weight, mu, float(eps)
+        self.width = weight.shape[0]
+
+    def cache_need(self):
+        return StateNeed((2, self.width), torch.float32)
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, *, ctx, state: torch.Tensor) -> torch.Tensor:
+        ops.rmsnorm_shift(x, self.weight, self.mu, self.eps, state, ctx, out)
         return out

@@ -29,14 +29,18 @@ class LearnedAbsolutePositions:
 @register_part("position", "rotary")
 class RotaryPositions:
     """Rotation of queries and keys by position.  Of a vector's first `dims` entries, entry i is paired with entry
-    i + dims/2; at position p the pair (u, v) becomes (u cos a − v sin a, v cos a + u sin a) with a = p · f_i and
+    i + dims/2 (`pairing` "half") or entry 2i with entry 2i + 1 (`pairing` "interleaved"); at position p the pair
+    (u, v) becomes (u cos a − v sin a, v cos a + u sin a) with a = p · f_i and
     f_i = base^(−2i/dims); entries beyond `dims` pass unchanged.  `scaling_factor` divides every frequency (linear
     scaling: positions count `scaling_factor` times slower).  The part holds the table f (float32, made in 64-bit);
     the mixer that is given the part applies it inside its own kernels, with angles in float32."""
 
     where = "qk"
 
-    def __init__(self, base: float, dims: int, device, scaling_factor: float = 1.0):
+    def __init__(self, base: float, dims: int, device, scaling_factor: float = 1.0, pairing: str = "half"):
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"RotaryPositions: pairing '{pairing}' is neither 'half' nor 'interleaved'")
+        self.pairing, self.interleaved = pairing, pairing == "interleaved"
         if dims <= 0 or dims % 2 != 0 or not base > 0.0:
             raise ValueError(f"RotaryPositions: {dims} dimensions cannot be rotated in pairs, or base {base} is not positive")
         if not scaling_factor > 0.0:
