@@ -696,21 +696,175 @@ def kotisun_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
     return out
 
 
+#: Rakelorn at two sizes that resemble a real model's layers, beside a Kuvusun of the same width, heads, latent sizes and
+#: experts (its closest relative in the framework: latent attention and routed experts) with as many layers as Rakelorn
+#: has layer runs.  Rakelorn: attention, recurrence, attention, attention, the recurrence's layer running twice; every
+#: layer with routed experts, of which the last `identity` router outputs return their input.
+RAKELORN_SIZES = {
+    "s": dict(DESIGN_SIZES["s"], gru=1024, identity=2, groups=3, keep=2),
+    "m": dict(DESIGN_SIZES["m"], gru=2048, identity=4, groups=4, keep=2),
+}
+
+
+def rakelorn_config(z: dict) -> dict:
+    att = {"type": "latent_attention", "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"],
+                                                 "kv_rank": z["kv_rank"], "q_rank": z["q_rank"], "scale": (z["dim"] + z["rot"]) ** -0.5,
+                                                 "rot": {"base": 10000.0, "dims": z["rot"]}}}
+    gru = {"type": "mingru", "mixer": {"width": z["gru"]}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.0,
+                      "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    return {"architecture": "Rakelorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [dict(att, mlp=moe), dict(gru, mlp=moe), dict(att, mlp=moe), dict(att, mlp=moe)]}
+
+
+def kuvusun_config_like(z: dict) -> dict:
+    """A Kuvusun of five layers (Rakelorn's layer runs), each with a rotated part, a gate and routed experts without a shared one."""
+    m = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "rot_dim": z["rot"],
+         "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    return {"architecture": "Kuvusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4},
+            "layers": [{"type": "latent_attention_2", "mixer": m, "mlp": moe}] * 5}
+
+
+def rakelorn_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
+    """Rakelorn's own kernels alone, each beside the like kernel of Kuvusun at equal size (timed as in `design_kernels`): the
+    norm with its token shift beside the norm in groups, the gated recurrence beside the element-wise gate, the router by
+    scores beside the router by logits, the weighted sum with identity experts beside the one without, the gate per head
+    beside the gate per column, and an expert's first product without a gate beside the gated one.  Attention, the
+    products per head and the grouped products are the kernels that Kuvusun runs (`--design kuvusun` measures them)."""
+    import types
+    import torch
+    from vlrf_b200.csrc import ops
+    dev, bf = "cuda", torch.bfloat16
+    width, W, H, vdim = z["width"], z["gru"], z["heads"], z["vdim"]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+
+    def timed(fn, reps=20):
+        for i in range(3):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3           # microseconds a launch
+
+    def bytes_point(us, nbytes):
+        return {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3), "mib": round(nbytes / 2**20, 1)}
+
+    # (a fifth of a second of work first, so that the first kernel measured does not run at idle clocks)
+    warm = torch.zeros(4096, 4096, device=dev)
+    t_end = time.time() + 0.2
+    while time.time() < t_end:
+        warm.add_(1.0)
+        torch.cuda.synchronize()
+    del warm
+    out = {}
+    S, L, B = 2, 1024, 64
+    T = S * L
+    pctx = types.SimpleNamespace(n_tokens=T, max_new=L, n_seqs=S, seq_slot=i32(list(range(S))), seq_start=i32([0, L, 2 * L]), seq_pos0=i32([0, 0]),
+                                 tok_slot=i32([s for s in range(S) for _ in range(L)]), tok_pos=i32(list(range(L)) * S))
+    dctx = types.SimpleNamespace(n_tokens=B, max_new=1, n_seqs=B, seq_slot=i32(list(range(B))), seq_start=i32(list(range(B + 1))),
+                                 seq_pos0=i32([L] * B), tok_slot=i32(list(range(B))), tok_pos=i32([L] * B))
+    ones_w, mu = torch.ones(width, device=dev), torch.full((width,), 0.5, device=dev)
+    for label, c, rows in (("prompt", pctx, T), ("decode", dctx, B)):
+        # -- the first norm: RMS norm + token shift, beside Kuvusun's norm in groups (which adds to the residual) ---------------
+        n_x = max(2, int(300e6 // (rows * width * 4)) + 1)
+        xs = [torch.randn(rows, width, device=dev) for _ in range(n_x)]
+        state = torch.zeros(max(S, B), 2, width, device=dev)
+        h = torch.zeros(rows, width, dtype=bf, device=dev)
+        us = timed(lambda i: ops.rmsnorm_shift(xs[i % n_x], ones_w, mu, 1e-6, state, c, h))
+        out["norm_" + label] = {"rakelorn": bytes_point(us, rows * width * 6)}
+        acc = torch.zeros(rows, width, device=dev)
+        us = timed(lambda i: ops.group_rmsnorm(xs[i % n_x], ones_w, 1e-5, 4, acc, accumulate=True, also=h))
+        out["norm_" + label]["kuvusun"] = bytes_point(us, rows * width * 14)
+        del xs
+        # -- the recurrence beside an element-wise gate over as many rows (Kuvusun's like kernel: nothing of it recurs) --------
+        n_p = max(2, int(300e6 // (rows * 3 * W * 4)) + 1)
+        projs = [torch.randn(rows, 3 * W, device=dev) for _ in range(n_p)]
+        st = torch.zeros(max(S, B), 2, W, device=dev)
+        g = torch.zeros(rows, W, dtype=bf, device=dev)
+        us = timed(lambda i: ops.mingru_scan(projs[i % n_p], 0, W, 2 * W, W, st, c, g))
+        out["recurrence_" + label] = {"rakelorn": bytes_point(us, rows * W * 14)}
+        us = timed(lambda i: ops.gate_mul(projs[i % n_p][:, :W], projs[i % n_p][:, W:2 * W], g, "silu", rows, W))
+        out["recurrence_" + label]["kuvusun_gate"] = bytes_point(us, rows * W * 10)
+        del projs
+        # -- the router and the weighted sum ------------------------------------------------------------------------------
+        E, n_id, top = z["experts"], z["identity"], z["top"]
+        zl = torch.randn(rows, E + n_id, device=dev)
+        ids = torch.zeros(rows, top, dtype=torch.int32, device=dev)
+        rank, row_of = torch.zeros_like(ids), torch.zeros_like(ids)
+        wts = torch.zeros(rows, top, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        corr = torch.zeros(E + n_id, device=dev)
+        us = timed(lambda i: (counts.zero_(), ops.moe_route_scored(zl, E + n_id, top, z["groups"], z["keep"], n_id, 2.0, corr, None, ids, wts, rank, counts, rows)))
+        us0 = timed(lambda i: counts.zero_())
+        out["router_" + label] = {"rakelorn": {"us": round(us - us0, 1)}}
+        us = timed(lambda i: (counts.zero_(), ops.moe_route(zl, E, top, False, None, ids, wts, rank, None, counts, rows)))
+        out["router_" + label]["kuvusun"] = {"us": round(us - us0, 1)}
+        counts.zero_()
+        ops.moe_route_scored(zl, E + n_id, top, z["groups"], z["keep"], n_id, 2.0, corr, None, ids, wts, rank, counts, rows)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+        ops.moe_plan(counts, offsets, E)
+        hin = torch.randn(rows, width, device=dev).to(bf)
+        sorted_rows = torch.zeros(rows * top, width, dtype=bf, device=dev)
+        ops.moe_gather(hin, ids, rank, offsets, sorted_rows, row_of, rows, top)
+        n_e = max(2, int(300e6 // (rows * top * width * 4)) + 1)
+        eos = [torch.randn(rows * top, width, device=dev) for _ in range(n_e)]
+        y = torch.zeros(rows, width, device=dev)
+        us = timed(lambda i: ops.moe_combine(eos[i % n_e], row_of, wts, top, None, None, y, rows, residual=y, ids=ids, h=hin))
+        out["combine_" + label] = {"rakelorn": bytes_point(us, rows * width * (4 * top + 8 + 2))}
+        us = timed(lambda i: ops.moe_combine(eos[i % n_e], row_of, wts, top, None, None, y, rows, residual=y))
+        out["combine_" + label]["kuvusun"] = bytes_point(us, rows * width * (4 * top + 8))
+        del eos
+        # -- the gate on the merged heads: a logit per head beside a logit per column ---------------------------------------
+        merged = torch.randn(rows, H * vdim, device=dev).to(bf)
+        gl = torch.randn(rows, H * vdim, device=dev)
+        us = timed(lambda i: ops.gate_mul(gl[:, :H], merged, merged, "sigmoid", rows, H * vdim, per=vdim))
+        out["head_gate_" + label] = {"rakelorn": bytes_point(us, rows * H * vdim * 4)}
+        us = timed(lambda i: ops.gate_mul(gl, merged, merged, "sigmoid", rows, H * vdim))
+        out["head_gate_" + label]["kuvusun"] = bytes_point(us, rows * H * vdim * 8)
+        # -- an expert's first product and its activation: up + relu² beside gate+up + silu·up, rows dealt evenly -----------------
+        ff = z["expert_ff"]
+        P = rows * top
+        x = torch.randn(P, width, device=dev).to(bf)
+        offs = i32([P * e // E for e in range(E + 1)])
+        w1 = (torch.randn(E, ff, width, device=dev) * 0.02).to(bf)
+        w2 = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
+        u1, u2 = torch.zeros(P, ff, dtype=bf, device=dev), torch.zeros(P, 2 * ff, dtype=bf, device=dev)
+        a = torch.zeros(P, ff, dtype=bf, device=dev)
+        us = timed(lambda i: (ops.linear_grouped(x, w1, u1, offs, P), ops.gate_mul(u1, u1, a, "relu", P, ff)))
+        fl = 2.0 * P * ff * width
+        out["expert_in_" + label] = {"rakelorn": {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 3),
+                                                  "gb_s": round(E * ff * width * 2 / us / 1e3, 1), "frac_hbm": round(E * ff * width * 2 / us / 1e3 / hbm_gbs, 3)}}
+        us = timed(lambda i: (ops.linear_grouped(x, w2, u2, offs, P), ops.gate_mul(u2[:, :ff], u2[:, ff:], a, "silu", P, ff)))
+        out["expert_in_" + label]["kuvusun"] = {"us": round(us, 1), "tflops": round(2 * fl / us / 1e6, 1), "frac_tensor": round(2 * fl / us / 1e6 / bf16_tflops, 3),
+                                                "gb_s": round(E * 2 * ff * width * 2 / us / 1e3, 1), "frac_hbm": round(E * 2 * ff * width * 2 / us / 1e3 / hbm_gbs, 3)}
+        del w1, w2
+    return out
+
+
 def design_bench(args) -> int:
-    """`--design NAME`: the design at sizes like a real model's layers (random weights) beside a GPT-2 of equal
-    size: prefill and decode throughput, and each kernel's time.  One JSON line."""
+    """`--design NAME`: the design at sizes like a real model's layers (random weights) beside its closest existing
+    model of equal size (GPT-2; for Rakelorn, Kuvusun): prefill and decode throughput, and each kernel's time.  One JSON line."""
     import vlrf_b200.models  # noqa: F401
     from vlrf_b200.weights import write_random_model
     hbm_gbs, bf16_tflops, peak_src = peaks()
     line = {"design": args.design, "beside": "gpt2", "dtype": "bf16", "data": "synthetic (seeded random token ids, random weights)",
             "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": {}}
     sizes, config_of, kernels_of = {"kuvusun": (DESIGN_SIZES, kuvusun_config, design_kernels),
-                                    "kotisun": (KOTISUN_SIZES, kotisun_config, kotisun_kernels)}[args.design]
+                                    "kotisun": (KOTISUN_SIZES, kotisun_config, kotisun_kernels),
+                                    "rakelorn": (RAKELORN_SIZES, rakelorn_config, rakelorn_kernels)}[args.design]
+    beside, beside_of = ("kuvusun", kuvusun_config_like) if args.design == "rakelorn" else ("gpt2", gpt2_config_like)
+    line["beside"] = beside
     for name in args.design_sizes.split(","):
         z = sizes[name]
         point = {"sizes": z}
         with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
-            for label, cfg in (() if args.design_only_kernels else ((args.design, config_of(z)), ("gpt2", gpt2_config_like(z)))):
+            for label, cfg in (() if args.design_only_kernels else ((args.design, config_of(z)), (beside, beside_of(z)))):
                 d = str(write_random_model(cfg, 1234, os.path.join(tmp, label)))
                 point[label] = design_point(d, args.design_prompt, [8, 64], max(8, min(args.steps, 64)), max(3, min(args.warmup, 8)))
         if not args.design_no_kernels:
@@ -765,8 +919,9 @@ def main() -> int:
                     help="with --only decode or prefill and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
-    ap.add_argument("--design", default=None, choices=["kuvusun", "kotisun"],
-                    help="instead of the default workload: this design at sizes like a real model's layers beside a GPT-2 of equal size")
+    ap.add_argument("--design", default=None, choices=["kuvusun", "kotisun", "rakelorn"],
+                    help="instead of the default workload: this design at sizes like a real model's layers beside its closest "
+                         "existing model of equal size (GPT-2; for rakelorn, Kuvusun)")
     ap.add_argument("--design-sizes", default="s,m", help="with --design: which of the sizes %s" % ",".join(DESIGN_SIZES))
     ap.add_argument("--design-no-kernels", action="store_true", help="with --design: whole steps only, not each kernel alone")
     ap.add_argument("--design-only-kernels", action="store_true", help="with --design: each kernel alone only")

@@ -56,7 +56,7 @@ _SIGNATURES = {
                           _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_gemm_tcgen05_groups_takes": [_c_int] * 9,
     "vlrf_gemm_tcgen05_groups": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_prefill_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_attn_prefill": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
@@ -118,7 +118,7 @@ _SIGNATURES = {
     "vlrf_gemm_heads": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_void_p],
     "vlrf_gemm_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                          _c_void_p],
+                          _c_int, _c_void_p],
     "vlrf_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_void_p, _c_int,
                            _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_latent_q_rows": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,

@@ -18,7 +18,7 @@ constexpr int HBM = 64, HBN = 64, HBK = 16, HTM = 4, HTN = 4, HTHREADS = 256;
 template <typename IT, typename OT>
 __device__ __forceinline__ void tile_product(const IT* __restrict__ X, const IT* __restrict__ W, OT* __restrict__ Y, int m0,
                                              int m_end, int n0, int N, int K, int ldx, int ldy, float (*As)[HBM + 4],
-                                             float (*Bs)[HBN + 4]) {
+                                             float (*Bs)[HBN + 4], int act = VLRF_ACT_NONE) {
     const int tid = threadIdx.x;
     const int lr = tid >> 2, lk = (tid & 3) * 4;
     const int ty = tid >> 4, tx = tid & 15;
@@ -57,7 +57,7 @@ __device__ __forceinline__ void tile_product(const IT* __restrict__ X, const IT*
 #pragma unroll
         for (int j = 0; j < HTN; ++j) {
             const int n = n0 + tx * HTN + j;
-            if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, acc[i][j]);
+            if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, apply_act_rt(acc[i][j], act));
         }
     }
 }
@@ -78,7 +78,7 @@ gemm_heads_kernel(const IT* __restrict__ X, int ldx, int x_hs, const IT* __restr
 template <typename IT, typename OT>
 __global__ void __launch_bounds__(HTHREADS)
 gemm_grouped_kernel(const IT* __restrict__ X, const IT* __restrict__ W, OT* __restrict__ Y, const int* __restrict__ offsets,
-                    int G, int N, int K) {
+                    int G, int N, int K, int act) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
     __shared__ float As[HBK][HBM + 4];
@@ -96,7 +96,7 @@ gemm_grouped_kernel(const IT* __restrict__ X, const IT* __restrict__ W, OT* __re
     }
     __syncthreads();
     if (where[1] < 0) return;                                  // beyond the last group's tiles
-    tile_product<IT, OT>(X, W + (size_t)where[0] * N * K, Y, where[1], where[2], blockIdx.x * HBN, N, K, K, N, As, Bs);
+    tile_product<IT, OT>(X, W + (size_t)where[0] * N * K, Y, where[1], where[2], blockIdx.x * HBN, N, K, K, N, As, Bs, act);
 }
 }  // namespace
 
@@ -117,12 +117,13 @@ extern "C" int vlrf_gemm_heads(const void* X, int ldx, int x_hs, const void* W, 
 }
 
 extern "C" int vlrf_gemm_grouped(const void* X, const void* W, void* Y, const int* offsets, int G, int P, int N, int K,
-                                 int in_dtype, int out_dtype, cudaStream_t stream) {
+                                 int in_dtype, int out_dtype, int act, cudaStream_t stream) {
+    VLRF_REQUIRE(act >= 0 && act <= VLRF_ACT_LAST_FUSED, "gemm_grouped: activation %d is not taken", act);
     VLRF_REQUIRE(P >= 0 && N > 0 && K > 0 && G > 0 && offsets != nullptr, "gemm_grouped: bad sizes P=%d N=%d K=%d G=%d", P, N, K, G);
     if (P == 0) return VLRF_OK;
     dim3 grid((N + HBN - 1) / HBN, (P + HBM - 1) / HBM + G);
     VLRF_REQUIRE(grid.y <= 65535, "gemm_grouped: too many row tiles");
-#define LAUNCH(IT, OT) launch_chained(gemm_grouped_kernel<IT, OT>, dim3(grid), dim3(HTHREADS), (size_t)(0), stream, (const IT*)X, (const IT*)W, (OT*)Y, offsets, G, N, K)
+#define LAUNCH(IT, OT) launch_chained(gemm_grouped_kernel<IT, OT>, dim3(grid), dim3(HTHREADS), (size_t)(0), stream, (const IT*)X, (const IT*)W, (OT*)Y, offsets, G, N, K, act)
     if (in_dtype == VLRF_F32 && out_dtype == VLRF_F32) LAUNCH(float, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_F32) LAUNCH(__nv_bfloat16, float);
     else if (in_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -531,7 +531,7 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
 // ---- a weight matrix per group: experts over rows sorted by expert, or heads with columns of their own --------------
 namespace {
 template <int BN, int STAGES, typename OT>
-int launch_tc_groups(const void* X, int ldx, const void* W, void* Y, int ldy, const TcGroups& gr, int N, int K, int* dev_err,
+int launch_tc_groups(const void* X, int ldx, const void* W, void* Y, int ldy, const TcGroups& gr, int N, int K, int act, int* dev_err,
                      cudaStream_t stream) {
     CUtensorMap tx, tw;
     const long long x_cols = gr.offsets ? K : (long long)(gr.G - 1) * gr.x_gs + K;
@@ -553,7 +553,7 @@ int launch_tc_groups(const void* X, int ldx, const void* W, void* Y, int ldy, co
     const int sms = sm_count_cached();
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, (const float*)nullptr, (const float*)nullptr,
-                                   (OT*)Y, gr.rows, N, K, ldy, (int)VLRF_ACT_NONE, TcKvScatter{}, dev_err, vlrf_trace_buffer(), gr);
+                                   (OT*)Y, gr.rows, N, K, ldy, act, TcKvScatter{}, dev_err, vlrf_trace_buffer(), gr);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05_groups: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_tcgen05_groups");
 }
@@ -569,19 +569,21 @@ extern "C" int vlrf_gemm_tcgen05_groups_takes(int rows, int G, int N, int K, int
 
 // offsets != null: rows offsets[g] … offsets[g+1]−1 of X [rows][K] times W[g]ᵀ into the same rows of Y [rows][N]
 // (x_gs = y_gs = 0).  offsets == null: every group (head) multiplies all rows, reading X at column g·x_gs and writing Y at
-// column g·y_gs.  W [G][N][K]; X and W bfloat16, Y bfloat16 or float32; no bias, activation or residual.
+// column g·y_gs.  W [G][N][K]; X and W bfloat16, Y bfloat16 or float32; an activation (VLRF_ACT_NONE, _GELU_TANH or _RELU2) on
+// the result, no bias or residual.
 extern "C" int vlrf_gemm_tcgen05_groups(const void* X, int ldx, int x_gs, const void* W, void* Y, int ldy, int y_gs,
-                                        const int* offsets, int G, int rows, int N, int K, int out_dtype, int* dev_err,
+                                        const int* offsets, int G, int rows, int N, int K, int out_dtype, int act, int* dev_err,
                                         cudaStream_t stream) {
+    VLRF_REQUIRE(act == VLRF_ACT_NONE || act == VLRF_ACT_GELU_TANH || act == VLRF_ACT_RELU2, "gemm_tcgen05_groups: activation %d is not taken", act);
     VLRF_REQUIRE(vlrf_gemm_tcgen05_groups_takes(rows, G, N, K, ldx, x_gs, ldy, y_gs, offsets != nullptr),
                  "gemm_tcgen05_groups: does not take rows=%d G=%d N=%d K=%d ldx=%d x_gs=%d ldy=%d y_gs=%d", rows, G, N, K, ldx, x_gs, ldy, y_gs);
     VLRF_REQUIRE(dev_err != nullptr && (out_dtype == VLRF_BF16 || out_dtype == VLRF_F32), "gemm_tcgen05_groups: bad arguments");
     VLRF_REQUIRE((reinterpret_cast<uintptr_t>(Y) & 15) == 0, "gemm_tcgen05_groups: Y must start on a 16-byte boundary");
     const TcGroups gr{offsets, G, x_gs, y_gs, rows};
     if (N <= 64) {
-        return out_dtype == VLRF_BF16 ? launch_tc_groups<64, 4, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream)
-                                      : launch_tc_groups<64, 4, float>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream);
+        return out_dtype == VLRF_BF16 ? launch_tc_groups<64, 4, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, act, dev_err, stream)
+                                      : launch_tc_groups<64, 4, float>(X, ldx, W, Y, ldy, gr, N, K, act, dev_err, stream);
     }
-    return out_dtype == VLRF_BF16 ? launch_tc_groups<128, 3, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream)
-                                  : launch_tc_groups<128, 3, float>(X, ldx, W, Y, ldy, gr, N, K, dev_err, stream);
+    return out_dtype == VLRF_BF16 ? launch_tc_groups<128, 3, __nv_bfloat16>(X, ldx, W, Y, ldy, gr, N, K, act, dev_err, stream)
+                                  : launch_tc_groups<128, 3, float>(X, ldx, W, Y, ldy, gr, N, K, act, dev_err, stream);
 }

@@ -653,15 +653,17 @@ def linear_heads(x, w, out, n_rows: int) -> None:
         from . import library
         if library().vlrf_gemm_tcgen05_groups_takes(n_rows, H, N, K, x.stride(0), x.stride(1), out.stride(0), out.stride(1), 0):
             call("vlrf_gemm_tcgen05_groups", _ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1),
-                 0, H, n_rows, N, K, dtype_code(out.dtype), _ptr(_dev_err()), _stream())
+                 0, H, n_rows, N, K, dtype_code(out.dtype), 0, _ptr(_dev_err()), _stream())
             return
     call("vlrf_gemm_heads", _ptr(x), x.stride(0), x.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1), n_rows, N, K,
          H, dtype_code(x.dtype), dtype_code(out.dtype), _stream())
 
 
-def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
+def linear_grouped(x, w, out, offsets, n_rows: int, act=None) -> None:
     """Rows offsets[g] … offsets[g+1]−1 of x [P, K] times w[g]ᵀ (w [G, N, K]) into the same rows of out [P, N];
-    offsets: int32 [G + 1] on the device."""
+    offsets: int32 [G + 1] on the device.  act: None, "gelu_tanh" or "relu2" on the result."""
+    if act not in (None, "none", "gelu_tanh", "relu2"):
+        raise KernelError(f"linear_grouped: activation '{act}' is not taken")
     _dev(x, "x"); _dev(w, "w", x.dtype); _dev(out, "out"); _dev(offsets, "offsets", torch.int32)
     G, N, K = w.shape
     if x.shape[1] != K or out.shape[1] != N or min(x.shape[0], out.shape[0]) < n_rows or offsets.numel() < G + 1:
@@ -670,10 +672,10 @@ def linear_grouped(x, w, out, offsets, n_rows: int) -> None:
         from . import library
         if library().vlrf_gemm_tcgen05_groups_takes(n_rows, G, N, K, K, 0, N, 0, 1):
             call("vlrf_gemm_tcgen05_groups", _ptr(x), K, 0, _ptr(w), _ptr(out), N, 0, _ptr(offsets), G, n_rows, N, K,
-                 dtype_code(out.dtype), _ptr(_dev_err()), _stream())
+                 dtype_code(out.dtype), ACT[act], _ptr(_dev_err()), _stream())
             return
     call("vlrf_gemm_grouped", _ptr(x), _ptr(w), _ptr(out), _ptr(offsets), G, n_rows, N, K, dtype_code(x.dtype),
-         dtype_code(out.dtype), _stream())
+         dtype_code(out.dtype), ACT[act], _stream())
 
 
 # ---- attention over a cache of latents --------------------------------------------------------------------------------

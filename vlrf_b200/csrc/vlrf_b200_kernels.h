@@ -92,10 +92,11 @@ int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias, const flo
 // The same kernel with a weight matrix per group.  offsets != null (device, G + 1 entries): rows offsets[g] …
 // offsets[g+1]−1 of X [rows][K] times W[g]ᵀ into the same rows of Y [rows][N] (experts over rows sorted by expert;
 // x_gs = y_gs = 0).  offsets == null: every group multiplies all rows, reading X at column g·x_gs and writing Y at
-// column g·y_gs (heads).  W [G][N][K]; no bias, activation, residual or scatter.
+// column g·y_gs (heads).  W [G][N][K]; an activation on the result (VLRF_ACT_NONE, _GELU_TANH, _RELU2); no bias,
+// residual or scatter.
 int vlrf_gemm_tcgen05_groups_takes(int rows, int G, int N, int K, int ldx, int x_gs, int ldy, int y_gs, int by_offsets);
 int vlrf_gemm_tcgen05_groups(const void* X, int ldx, int x_gs, const void* W, void* Y, int ldy, int y_gs, const int* offsets,
-                             int G, int rows, int N, int K, int out_dtype, int* dev_err, cudaStream_t stream);
+                             int G, int rows, int N, int K, int out_dtype, int act, int* dev_err, cudaStream_t stream);
 // For measurements: force the tile width (64 … 256 in steps of 32), 0 = chosen by size again.
 int vlrf_gemm_tcgen05_force_width(int bn);
 
@@ -273,9 +274,9 @@ int vlrf_ssd_gate_norm(const float* y, const float* proj, int ld, int z_off, con
 int vlrf_gemm_heads(const void* X, int ldx, int x_hs, const void* W, void* Y, int ldy, int y_hs, int M, int N, int K, int H,
                     int in_dtype, int out_dtype, cudaStream_t stream);
 // Rows offsets[g] … offsets[g+1]−1 of X [P][K] times W[g]ᵀ ([G][N][K]) into the same rows of Y [P][N]; offsets
-// (G + 1 entries, ascending, offsets[G] ≤ P) on the device.
+// (G + 1 entries, ascending, offsets[G] ≤ P) on the device; act: an activation on the result.
 int vlrf_gemm_grouped(const void* X, const void* W, void* Y, const int* offsets, int G, int P, int N, int K, int in_dtype,
-                      int out_dtype, cudaStream_t stream);
+                      int out_dtype, int act, cudaStream_t stream);
 
 // ---- attention over a cache of latents (attention_latent.cu) -----------------------------------------------------------
 // The cache of one layer is [n_blocks][BT][row_w] of `dtype`: per token a row [c | r], the normed latent (C numbers)

@@ -132,9 +132,7 @@ class RoutedExperts:
                 ops.linear_grouped(rows, self.w_gate_up, u, offsets, P)
                 ops.gate_mul(u[:, :ff], u[:, ff:], a, "silu", P, ff)
             else:
-                u = ws.get("moe_gate_up", P, ff, act)
-                ops.linear_grouped(rows, self.w_gate_up, u, offsets, P)
-                ops.gate_mul(u, u, a, "relu", P, ff)                     # relu(u) · u = relu(u)²
+                ops.linear_grouped(rows, self.w_gate_up, a, offsets, P, act="relu2")     # (the activation in the product's epilogue)
             ops.linear_grouped(a, self.w_down, out, offsets, P)
         shared_out = None
         if self.shared is not None:
