@@ -16,7 +16,8 @@
 #include "common.cuh"
 
 namespace {
-constexpr int SCAN_WARPS = 16;
+constexpr int SCAN_WARPS = 32;
+constexpr int SCAN_BATCH = 8;             // tokens whose inputs a lane asks for together
 
 __device__ __forceinline__ float candidate_f(float u) { return u >= 0.f ? u + 0.5f : sigmoid_f(u); }
 
@@ -61,11 +62,20 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     const float* p = proj + (size_t)row0 * ld + (live ? ch : 0);
     float A = 1.f, B = 0.f;
     if (live) {
-#pragma unroll 4
-        for (int t = a; t < b; ++t) {
-            const float z = sigmoid_f(p[(size_t)t * ld + z_off]), c = candidate_f(p[(size_t)t * ld + u_off]);
-            A *= 1.f - z;
-            B = fmaf(z, c - B, B);
+        for (int t0 = a; t0 < b; t0 += SCAN_BATCH) {
+            float zl[SCAN_BATCH], ul[SCAN_BATCH];
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {             // (beyond the run: a gate that is shut changes nothing)
+                const bool in = t0 + k < b;
+                zl[k] = in ? p[(size_t)(t0 + k) * ld + z_off] : -INFINITY;
+                ul[k] = in ? p[(size_t)(t0 + k) * ld + u_off] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {
+                const float z = sigmoid_f(zl[k]), c = candidate_f(ul[k]);
+                A *= 1.f - z;
+                B = fmaf(z, c - B, B);
+            }
         }
     }
     A_sm[warp][lane] = A;
@@ -82,11 +92,21 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     if (live && warp == 0) state[((size_t)slot * 2 + ((pos0 + n) & 1)) * W + ch] = S_end;
     if (!live) return;
     OT* o = out + (size_t)row0 * ld_out + ch;
-#pragma unroll 4
-    for (int t = a; t < b; ++t) {
-        const float z = sigmoid_f(p[(size_t)t * ld + z_off]), c = candidate_f(p[(size_t)t * ld + u_off]), g = p[(size_t)t * ld + g_off];
-        S = fmaf(z, c - S, S);
-        ElemIO<OT>::store(o + (size_t)t * ld_out, S * silu_f(g));
+    for (int t0 = a; t0 < b; t0 += SCAN_BATCH) {
+        float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH];
+#pragma unroll
+        for (int k = 0; k < SCAN_BATCH; ++k) {
+            const bool in = t0 + k < b;
+            zl[k] = in ? p[(size_t)(t0 + k) * ld + z_off] : -INFINITY;
+            ul[k] = in ? p[(size_t)(t0 + k) * ld + u_off] : 0.f;
+            gl[k] = in ? p[(size_t)(t0 + k) * ld + g_off] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < SCAN_BATCH; ++k) {
+            const float z = sigmoid_f(zl[k]), c = candidate_f(ul[k]);
+            S = fmaf(z, c - S, S);
+            if (t0 + k < b) ElemIO<OT>::store(o + (size_t)(t0 + k) * ld_out, S * silu_f(gl[k]));
+        }
     }
 }
 }  // namespace

@@ -19,8 +19,8 @@
 // (zeros ahead of the first).  The token before is the row above where the step brings it, else the sequence's kept
 // row: a float32 state [slot][2][d] holds the normed row of each sequence's last token twice, a step reading the copy
 // of the parity of the position it begins at and writing the copy of the parity of the position it ends at, so a step
-// of one token leaves what it read and may run twice.  The CTA of a sequence's first token of the step also norms the
-// sequence's last row of the step and keeps it, after it has read the kept row itself.
+// of one token leaves what it read and may run twice.  The warp of a sequence's first token of the step also norms the
+// sequence's last row of the step and keeps it, each lane after its own read of the kept row.
 //
 // add_row_vector: x[t] += v for every row (a vector that a model adds to the residual between layers).
 #include "common.cuh"
@@ -110,6 +110,27 @@ __global__ void gate_mul_f32x4_kernel(const float* a, int lda, const float* b, i
     *reinterpret_cast<uint2*>(out + (size_t)r * ldo + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
 }
 
+// a float32 gate logit per group of `per` columns (per a multiple of 8), bfloat16 values and result, eight a thread
+__global__ void gate_mul_groups_bf16x8_kernel(const float* a, int lda, const __nv_bfloat16* b, int ldb, __nv_bfloat16* out, int ldo,
+                                              int rows, int cols8, int per8, int act) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols8) return;
+    const int r = (int)(i / cols8), c8 = (int)(i - (long long)r * cols8);
+    const float f = gate_f(act, a[(size_t)r * lda + c8 / per8]);
+    const uint4 va = *reinterpret_cast<const uint4*>(b + (size_t)r * ldb + c8 * 8);
+    const uint32_t vw[4] = {va.x, va.y, va.z, va.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float v0 = __uint_as_float(vw[k] << 16), v1 = __uint_as_float(vw[k] & 0xffff0000u);
+        const __nv_bfloat162 p = __floats2bfloat162_rn(f * v0, f * v1);
+        o[k] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <typename AT, typename BT, typename OT>
 __global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, int act, int per) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
@@ -123,48 +144,59 @@ __global__ void gate_mul_kernel(const AT* a, int lda, const BT* b, int ldb, OT* 
     ElemIO<OT>::store(out + (size_t)r * ldo + c, f * v);
 }
 
-// the inverse root mean square of a float32 row, by the whole CTA (every thread gets it)
-__device__ __forceinline__ float row_inv_rms(const float* __restrict__ row, int d, float eps, float* part) {
+// rmsnorm_shift: a warp per token.  The warp sums the squares of its row, of the row above where that is the token before,
+// and (for a sequence's first row of the step) of the sequence's last row of the step, with shuffles only; the second
+// pass finds the rows in L1.  VEC: rows and outputs on 16-byte boundaries and d a multiple of 4, four values a lane.
+constexpr int SHIFT_WARPS = 4;
+
+template <bool VEC>
+__device__ __forceinline__ float warp_inv_rms(const float* __restrict__ row, int d, float eps, int lane) {
     float s = 0.f;
-    for (int i = threadIdx.x; i < d; i += NORM_THREADS) { const float v = row[i]; s = fmaf(v, v, s); }
+    if (VEC) {
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) { const float v = row[i]; s = fmaf(v, v, s); }
+    }
     s = warp_sum(s);
-    __syncthreads();                                           // (part may still be read from the row before)
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
-    __syncthreads();
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < NORM_THREADS / 32; ++w) total += part[w];
-    return 1.f / sqrtf(total / (float)d + eps);
+    return 1.f / sqrtf(s / (float)d + eps);
 }
 
-template <typename OT>
-__global__ void __launch_bounds__(NORM_THREADS)
+template <typename OT> __device__ __forceinline__ void store4(OT* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+template <typename OT, bool VEC>
+__global__ void __launch_bounds__(SHIFT_WARPS * 32)
 rmsnorm_shift_kernel(const float* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ mu, float eps,
                      float* state, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                      const int* __restrict__ seq_start, int n_seqs, int T, OT* __restrict__ out, int ld_out, int d) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
-    __shared__ float part[NORM_THREADS / 32];
-    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * SHIFT_WARPS + (threadIdx.x >> 5);
+    if (t >= T) return;                                        // (whole warps leave; no block-wide barrier below)
     const int slot = tok_slot[t];
     OT* o = out + (size_t)t * ld_out;
     if (slot < 0) {                                            // padding row
-        for (int i = threadIdx.x; i < d; i += NORM_THREADS) ElemIO<OT>::store(o + i, 0.f);
+        for (int i = lane; i < d; i += 32) ElemIO<OT>::store(o + i, 0.f);
         return;
     }
     const int pos = tok_pos[t];
     const bool row_above = t > 0 && tok_slot[t - 1] == slot;   // the token before came with this step
     const float* xr = x + (size_t)t * ld_x;
-    const float inv = row_inv_rms(xr, d, eps, part);
-    float inv_prev = 0.f;
-    const float* prev = nullptr;                               // where the token before lies: a row of x, the state, or nowhere
-    if (row_above) {
-        prev = xr - ld_x;
-        inv_prev = row_inv_rms(prev, d, eps, part);
-    } else if (pos > 0) {
-        prev = state + ((size_t)slot * 2 + (pos & 1)) * d;
-    }
-    // the row that the sequence keeps: that of its last token of this step, normed by the CTA of its first
+    const float inv = warp_inv_rms<VEC>(xr, d, eps, lane);
+    // where the token before lies: a row of x (normed here once more), the kept row, or nowhere (position 0)
+    const float* prev = row_above ? xr - ld_x : (pos > 0 ? state + ((size_t)slot * 2 + (pos & 1)) * d : nullptr);
+    const float inv_prev = row_above ? warp_inv_rms<VEC>(prev, d, eps, lane) : 1.f;
+    // the row that the sequence keeps: that of its last token of this step, normed by the warp of its first
     const float* last = nullptr;
     float inv_last = 0.f;
     float* keep = nullptr;
@@ -174,16 +206,34 @@ rmsnorm_shift_kernel(const float* __restrict__ x, int ld_x, const float* __restr
         const int end = (lo < n_seqs && seq_start[lo] == t) ? seq_start[lo + 1] : t + 1;
         const int n = min(end, T) - t;
         last = xr + (size_t)(n - 1) * ld_x;
-        inv_last = n > 1 ? row_inv_rms(last, d, eps, part) : inv;
+        inv_last = n > 1 ? warp_inv_rms<VEC>(last, d, eps, lane) : inv;
         keep = state + ((size_t)slot * 2 + ((pos + n) & 1)) * d;
     }
-    for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
-        const float g = w[i];
-        const float n_t = xr[i] * inv * g;
-        float n_prev = 0.f;
-        if (prev != nullptr) n_prev = row_above ? prev[i] * inv_prev * g : prev[i];
-        ElemIO<OT>::store(o + i, n_t + (n_prev - n_t) * mu[i]);
-        if (keep != nullptr) keep[i] = last[i] * inv_last * g;   // (after this thread's read of the kept row)
+    if (VEC) {
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 g = *reinterpret_cast<const float4*>(w + i), m = *reinterpret_cast<const float4*>(mu + i);
+            const float4 v = *reinterpret_cast<const float4*>(xr + i);
+            float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (prev != nullptr) pv = *reinterpret_cast<const float4*>(prev + i);
+            const float pg = row_above ? inv_prev : 1.f;       // (the kept row is normed already)
+            const float n0 = v.x * inv * g.x, n1 = v.y * inv * g.y, n2 = v.z * inv * g.z, n3 = v.w * inv * g.w;
+            const float p0 = row_above ? pv.x * pg * g.x : pv.x, p1 = row_above ? pv.y * pg * g.y : pv.y;
+            const float p2 = row_above ? pv.z * pg * g.z : pv.z, p3 = row_above ? pv.w * pg * g.w : pv.w;
+            store4<OT>(o + i, n0 + (p0 - n0) * m.x, n1 + (p1 - n1) * m.y, n2 + (p2 - n2) * m.z, n3 + (p3 - n3) * m.w);
+            if (keep != nullptr) {                             // (after this lane's read of the kept row)
+                const float4 l = *reinterpret_cast<const float4*>(last + i);
+                *reinterpret_cast<float4*>(keep + i) = make_float4(l.x * inv_last * g.x, l.y * inv_last * g.y, l.z * inv_last * g.z, l.w * inv_last * g.w);
+            }
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) {
+            const float g = w[i];
+            const float n_t = xr[i] * inv * g;
+            float n_prev = 0.f;
+            if (prev != nullptr) n_prev = row_above ? prev[i] * inv_prev * g : prev[i];
+            ElemIO<OT>::store(o + i, n_t + (n_prev - n_t) * mu[i]);
+            if (keep != nullptr) keep[i] = last[i] * inv_last * g;   // (after this lane's read of the kept row)
+        }
     }
 }
 
@@ -203,11 +253,15 @@ extern "C" int vlrf_rmsnorm_shift(const float* x, int ld_x, const float* w, cons
     VLRF_REQUIRE(T >= 0 && d > 0 && ld_x >= d && ld_out >= d && n_seqs >= 0, "rmsnorm_shift: bad sizes");
     VLRF_REQUIRE(x && w && mu && state && tok_slot && tok_pos && seq_start && out, "rmsnorm_shift: a null pointer");
     if (T == 0) return VLRF_OK;
-    if (out_dtype == VLRF_F32)
-        launch_chained(rmsnorm_shift_kernel<float>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (float*)out, ld_out, d);
-    else if (out_dtype == VLRF_BF16)
-        launch_chained(rmsnorm_shift_kernel<__nv_bfloat16>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (__nv_bfloat16*)out, ld_out, d);
+    const bool vec = d % 4 == 0 && ld_x % 4 == 0 && ld_out % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(mu) |
+                       reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const dim3 grid((unsigned)((T + SHIFT_WARPS - 1) / SHIFT_WARPS)), block(SHIFT_WARPS * 32);
+#define GO(OT, V) launch_chained(rmsnorm_shift_kernel<OT, V>, grid, block, (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (OT*)out, ld_out, d)
+    if (out_dtype == VLRF_F32) { if (vec) GO(float, true); else GO(float, false); }
+    else if (out_dtype == VLRF_BF16) { if (vec) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
     else return vlrf_fail(VLRF_ERR_INVALID_ARG, "rmsnorm_shift: unknown output dtype %d", out_dtype);
+#undef GO
     return vlrf_check_launch("rmsnorm_shift");
 }
 
@@ -273,7 +327,11 @@ static int gate_mul_any(const void* a, int lda, int a_dtype, const void* b, int 
                          cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
     typedef __nv_bfloat16 bf;
 #define GO(AT, BT, OT) launch_chained(gate_mul_kernel<AT, BT, OT>, blocks, dim3(256), (size_t)0, stream, (const AT*)a, lda, (const BT*)b, ldb, (OT*)out, ldo, rows, cols, act, per)
-    if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && aligned)
+    if (per > 1 && per % 8 == 0 && a_dtype == VLRF_F32 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && ldb % 8 == 0 && ldo % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+        launch_chained(gate_mul_groups_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), (size_t)0, stream, (const float*)a, lda,
+                       (const bf*)b, ldb, (bf*)out, ldo, rows, cols / 8, per / 8, act);
+    else if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && aligned)
         launch_chained(gate_mul_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), (size_t)0, stream, (const bf*)a, lda, (const bf*)b, ldb,
                        (bf*)out, ldo, rows, cols / 8, act);
     else if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(bf, bf, bf);
