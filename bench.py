@@ -728,7 +728,7 @@ def kuvusun_config_like(z: dict) -> dict:
 
 
 def rakelorn_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
-    """Rakelorn's own kernels alone, each beside the like kernel of Kuvusun at equal size (timed as in `design_kernels`): the
+    """Rakelorn's own kernels alone, each beside the like kernel of Kuvusun at equal size (20 launches replayed as one graph, inputs rotated over more than L2): the
     norm with its token shift beside the norm in groups, the gated recurrence beside the element-wise gate, the router by
     scores beside the router by logits, the weighted sum with identity experts beside the one without, the gate per head
     beside the gate per column, and an expert's first product without a gate beside the gated one.  Attention, the
@@ -741,16 +741,23 @@ def rakelorn_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
 
     def timed(fn, reps=20):
+        """Microseconds a launch: the `reps` launches are captured as one graph (as a step's kernels are when the engine
+        replays it), so that the host's time to issue a launch is no part of the number."""
         for i in range(3):
             fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        for i in range(reps):
-            fn(i)
+        graph.replay()
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps * 1e3           # microseconds a launch
+        return e0.elapsed_time(e1) / reps * 1e3
 
     def bytes_point(us, nbytes):
         return {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3), "mib": round(nbytes / 2**20, 1)}
@@ -834,9 +841,9 @@ def rakelorn_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
         offs = i32([P * e // E for e in range(E + 1)])
         w1 = (torch.randn(E, ff, width, device=dev) * 0.02).to(bf)
         w2 = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
-        u1, u2 = torch.zeros(P, ff, dtype=bf, device=dev), torch.zeros(P, 2 * ff, dtype=bf, device=dev)
+        u2 = torch.zeros(P, 2 * ff, dtype=bf, device=dev)
         a = torch.zeros(P, ff, dtype=bf, device=dev)
-        us = timed(lambda i: (ops.linear_grouped(x, w1, u1, offs, P), ops.gate_mul(u1, u1, a, "relu", P, ff)))
+        us = timed(lambda i: ops.linear_grouped(x, w1, a, offs, P, act="relu2"))       # (the activation in the product's epilogue)
         fl = 2.0 * P * ff * width
         out["expert_in_" + label] = {"rakelorn": {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 3),
                                                   "gb_s": round(E * ff * width * 2 / us / 1e3, 1), "frac_hbm": round(E * ff * width * 2 / us / 1e3 / hbm_gbs, 3)}}

@@ -70,7 +70,7 @@ def run_steps(fn, lengths_done, n_slots, width, out_dtype):
 
 
 @pytest.mark.parametrize("dt", DT)
-@pytest.mark.parametrize("d", [96, 100, 1024])
+@pytest.mark.parametrize("d", [96, 100, 1024, 2048, 4100, 8200])      # (rows held by 1, 2 and 4 quads a thread, by more threads; too wide: a warp a token)
 def test_norm_with_token_shift_over_steps(d, dt):
     from vlrf_b200.csrc import ops
     g = torch.Generator().manual_seed(d)
@@ -147,6 +147,42 @@ def test_gated_recurrence_over_steps(W, dt):
         close(got[i], want[i], tol(dt), f"sequence {i}")
     others = [s for s in range(8) if s not in SLOTS]
     assert torch.isnan(state[others]).all(), "a state of another slot was written"
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_gated_recurrence_of_long_unequal_prompts_in_one_step(dt):
+    """Prompts long enough that several CTAs share a sequence's tokens (the longest decides how many), beside a short one
+    and a single token; then a second portion that begins at an odd position, from the states the first left."""
+    from vlrf_b200.csrc import ops
+    W = 70
+    first, second = [1301, 37, 1, 600], [260, 3, 1030, 1]
+    g = torch.Generator().manual_seed(11)
+    projs = [torch.randn(a + b, 3 * W, generator=g, dtype=torch.float64) * 2 for a, b in zip(first, second)]
+    for p in projs:
+        p[:, :W] -= 2.0                                    # (gates that keep: a wrong state at a run's start shows for long)
+    want = []
+    for p in projs:
+        a, u, gg = p[:, :W], p[:, W:2 * W], p[:, 2 * W:]
+        S = plain.mingru_scan(torch.sigmoid(a), torch.where(u >= 0, u + 0.5, torch.sigmoid(u)))
+        want.append(S * gg * torch.sigmoid(gg))
+    slots = [5, 0, 3, 2]
+    state = torch.full((6, 2, W), float("nan"), device="cuda")
+    for s in slots:
+        state[s] = 0.0
+    got = [[] for _ in slots]
+    for part, lens in enumerate((first, second)):
+        p0s = [0] * 4 if part == 0 else first
+        ctx, _ = step_ctx([(s, p0, n) for s, p0, n in zip(slots, p0s, lens)])
+        rows = torch.cat([p[p0:p0 + n] for p, p0, n in zip(projs, p0s, lens)])
+        out = torch.zeros(ctx.n_tokens, W, dtype=dt, device="cuda")
+        ops.mingru_scan(dev(rows, torch.float32), 0, W, 2 * W, W, state, ctx, out)
+        at = 0
+        for i, n in enumerate(lens):
+            got[i].append(out[at:at + n].float().cpu())
+            at += n
+    for i in range(4):
+        close(torch.cat(got[i]), want[i], tol(dt), f"sequence {i}")
+    assert torch.isnan(state[[1, 4]]).all(), "a state of another slot was written"
 
 
 def test_gated_recurrence_keeps_a_far_token():

@@ -237,6 +237,95 @@ rmsnorm_shift_kernel(const float* __restrict__ x, int ld_x, const float* __restr
     }
 }
 
+// rmsnorm_shift with a CTA per token, for rows on 16-byte boundaries: a thread holds NV groups of four columns of its
+// row and of the row before in registers (both asked for at once), the two sums of squares are reduced together, and
+// nothing is read twice.  The CTA of a sequence's first token of the step also norms and keeps the sequence's last row.
+constexpr int SHIFT_ROW_MAX_NV = 4, SHIFT_ROW_MAX_THREADS = 512;     // rows of up to 8192 columns; wider ones a warp a token
+
+template <typename OT, int NV>
+__global__ void __launch_bounds__(NV == SHIFT_ROW_MAX_NV ? SHIFT_ROW_MAX_THREADS : 128)
+rmsnorm_shift_rows_kernel(const float* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ mu, float eps,
+                          float* state, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                          const int* __restrict__ seq_start, int n_seqs, int T, OT* __restrict__ out, int ld_out, int d) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    __shared__ float part[3][32];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int slot = tok_slot[t];
+    OT* o = out + (size_t)t * ld_out;
+    if (slot < 0) {                                            // padding row (the whole CTA)
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int i = 4 * (threadIdx.x + k * blockDim.x);
+            if (i < d) store4<OT>(o + i, 0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
+    const int pos = tok_pos[t];
+    const bool row_above = t > 0 && tok_slot[t - 1] == slot;   // the token before came with this step
+    const float* xr = x + (size_t)t * ld_x;
+    // where the token before lies: a row of x (normed here once more), the kept row, or nowhere (position 0)
+    const float* prev = row_above ? xr - ld_x : (pos > 0 ? state + ((size_t)slot * 2 + (pos & 1)) * d : nullptr);
+    // the row that the sequence keeps: that of its last token of this step, normed by the CTA of its first
+    const float* last = nullptr;
+    float* keep = nullptr;
+    if (!row_above) {
+        int lo = 0, hi = n_seqs;                               // the sequence whose rows begin at t
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (seq_start[mid] < t) lo = mid + 1; else hi = mid; }
+        const int end = (lo < n_seqs && seq_start[lo] == t) ? seq_start[lo + 1] : t + 1;
+        const int n = min(end, T) - t;
+        if (n > 1) last = xr + (size_t)(n - 1) * ld_x;         // (one token: the row in registers is the last)
+        keep = state + ((size_t)slot * 2 + ((pos + n) & 1)) * d;
+    }
+    float4 v[NV], pv[NV];
+    float s_own = 0.f, s_prev = 0.f, s_last = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        const bool in = i < d;
+        v[k] = in ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        pv[k] = (in && prev != nullptr) ? *reinterpret_cast<const float4*>(prev + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in && last != nullptr) {                           // (read again below: one CTA a sequence comes here)
+            const float4 l = *reinterpret_cast<const float4*>(last + i);
+            s_last = fmaf(l.x, l.x, s_last); s_last = fmaf(l.y, l.y, s_last); s_last = fmaf(l.z, l.z, s_last); s_last = fmaf(l.w, l.w, s_last);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        s_own = fmaf(v[k].x, v[k].x, s_own); s_own = fmaf(v[k].y, v[k].y, s_own); s_own = fmaf(v[k].z, v[k].z, s_own); s_own = fmaf(v[k].w, v[k].w, s_own);
+        s_prev = fmaf(pv[k].x, pv[k].x, s_prev); s_prev = fmaf(pv[k].y, pv[k].y, s_prev); s_prev = fmaf(pv[k].z, pv[k].z, s_prev); s_prev = fmaf(pv[k].w, pv[k].w, s_prev);
+    }
+    float4 gs[NV], ms[NV];                                     // asked for ahead of the barrier
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        gs[k] = i < d ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ms[k] = i < d ? *reinterpret_cast<const float4*>(mu + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    s_own = warp_sum(s_own); s_prev = warp_sum(s_prev); s_last = warp_sum(s_last);
+    if (lane == 0) { part[0][warp] = s_own; part[1][warp] = s_prev; part[2][warp] = s_last; }
+    __syncthreads();
+    float t_own = 0.f, t_prev = 0.f, t_last = 0.f;
+    for (int k = 0; k < n_warps; ++k) { t_own += part[0][k]; t_prev += part[1][k]; t_last += part[2][k]; }
+    const float inv = 1.f / sqrtf(t_own / (float)d + eps);
+    const float inv_prev = row_above ? 1.f / sqrtf(t_prev / (float)d + eps) : 1.f;      // (the kept row is normed already)
+    const float inv_last = last != nullptr ? 1.f / sqrtf(t_last / (float)d + eps) : inv;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i >= d) continue;
+        const float4 g = gs[k], m = ms[k];
+        const float n0 = v[k].x * inv * g.x, n1 = v[k].y * inv * g.y, n2 = v[k].z * inv * g.z, n3 = v[k].w * inv * g.w;
+        const float p0 = row_above ? pv[k].x * inv_prev * g.x : pv[k].x, p1 = row_above ? pv[k].y * inv_prev * g.y : pv[k].y;
+        const float p2 = row_above ? pv[k].z * inv_prev * g.z : pv[k].z, p3 = row_above ? pv[k].w * inv_prev * g.w : pv[k].w;
+        store4<OT>(o + i, n0 + (p0 - n0) * m.x, n1 + (p1 - n1) * m.y, n2 + (p2 - n2) * m.z, n3 + (p3 - n3) * m.w);
+        if (keep != nullptr) {                                 // (this thread has read these columns of the kept row)
+            const float4 l = last != nullptr ? *reinterpret_cast<const float4*>(last + i) : v[k];
+            *reinterpret_cast<float4*>(keep + i) = make_float4(l.x * inv_last * g.x, l.y * inv_last * g.y, l.z * inv_last * g.z, l.w * inv_last * g.w);
+        }
+    }
+}
+
 __global__ void add_row_vector_kernel(float* __restrict__ x, int ld, const float* __restrict__ v, int rows, int d) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
@@ -256,11 +345,24 @@ extern "C" int vlrf_rmsnorm_shift(const float* x, int ld_x, const float* w, cons
     const bool vec = d % 4 == 0 && ld_x % 4 == 0 && ld_out % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(mu) |
                        reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    VLRF_REQUIRE(out_dtype == VLRF_F32 || out_dtype == VLRF_BF16, "rmsnorm_shift: unknown output dtype %d", out_dtype);
+    const int quads = d / 4;
+    if (vec && quads <= SHIFT_ROW_MAX_NV * SHIFT_ROW_MAX_THREADS) {
+        // a CTA a token: a quad of columns a thread up to 128 threads, then more quads a thread, then more threads
+        int nv = 1, threads = 128;
+        while (nv < SHIFT_ROW_MAX_NV && nv * threads < quads) nv *= 2;
+        while (nv * threads < quads) threads *= 2;
+        threads = min(threads, ((quads + nv - 1) / nv + 31) / 32 * 32);
+#define ROWS(OT, NV) launch_chained(rmsnorm_shift_rows_kernel<OT, NV>, dim3(T), dim3(threads), (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (OT*)out, ld_out, d)
+        if (out_dtype == VLRF_F32) { if (nv == 1) ROWS(float, 1); else if (nv == 2) ROWS(float, 2); else ROWS(float, 4); }
+        else { if (nv == 1) ROWS(__nv_bfloat16, 1); else if (nv == 2) ROWS(__nv_bfloat16, 2); else ROWS(__nv_bfloat16, 4); }
+#undef ROWS
+        return vlrf_check_launch("rmsnorm_shift");
+    }
     const dim3 grid((unsigned)((T + SHIFT_WARPS - 1) / SHIFT_WARPS)), block(SHIFT_WARPS * 32);
 #define GO(OT, V) launch_chained(rmsnorm_shift_kernel<OT, V>, grid, block, (size_t)0, stream, x, ld_x, w, mu, eps, state, tok_slot, tok_pos, seq_start, n_seqs, T, (OT*)out, ld_out, d)
     if (out_dtype == VLRF_F32) { if (vec) GO(float, true); else GO(float, false); }
-    else if (out_dtype == VLRF_BF16) { if (vec) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
-    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "rmsnorm_shift: unknown output dtype %d", out_dtype);
+    else { if (vec) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
 #undef GO
     return vlrf_check_launch("rmsnorm_shift");
 }
