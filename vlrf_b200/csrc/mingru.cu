@@ -29,7 +29,12 @@ template <typename OT> struct Gate {
     static __device__ __forceinline__ float sigmoid(float x) { return sigmoid_f(x); }
 };
 template <> struct Gate<__nv_bfloat16> {
-    static __device__ __forceinline__ float sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+    static __device__ __forceinline__ float sigmoid(float x) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));      // e^(−x); ∞ for x = −∞
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+        return r;
+    }
 };
 template <typename OT> __device__ __forceinline__ float candidate_f(float u) { return u >= 0.f ? u + 0.5f : Gate<OT>::sigmoid(u); }
 template <typename OT> __device__ __forceinline__ float out_gate_f(float g) { return g * Gate<OT>::sigmoid(g); }
@@ -79,13 +84,29 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     const float* p = proj + (size_t)row0 * ld + (live ? ch : 0);
     float A = 1.f, B = 0.f;
     if (live) {
-        for (int t0 = a; t0 < b; t0 += SCAN_BATCH) {
+        const float* q = p + (size_t)a * ld;                   // the run's next token
+        int t0 = a;
+        for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld) {
+            float zl[SCAN_BATCH], ul[SCAN_BATCH];
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {
+                zl[k] = q[(size_t)k * ld + z_off];
+                ul[k] = q[(size_t)k * ld + u_off];
+            }
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {
+                const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                A *= 1.f - z;
+                B = fmaf(z, c - B, B);
+            }
+        }
+        if (t0 < b) {                                          // the run's last tokens, fewer than a batch
             float zl[SCAN_BATCH], ul[SCAN_BATCH];
 #pragma unroll
             for (int k = 0; k < SCAN_BATCH; ++k) {             // (beyond the run: a gate that is shut changes nothing)
                 const bool in = t0 + k < b;
-                zl[k] = in ? p[(size_t)(t0 + k) * ld + z_off] : -INFINITY;
-                ul[k] = in ? p[(size_t)(t0 + k) * ld + u_off] : 0.f;
+                zl[k] = in ? q[(size_t)k * ld + z_off] : -INFINITY;
+                ul[k] = in ? q[(size_t)k * ld + u_off] : 0.f;
             }
 #pragma unroll
             for (int k = 0; k < SCAN_BATCH; ++k) {
@@ -120,21 +141,38 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     S = fmaf(PA_sm[warp][lane], S, PB_sm[warp][lane]);         // the state ahead of this warp's run
     cluster_sync_relaxed();                                    // everyone has read the kept state and the totals
     if (live) {
-        OT* o = out + (size_t)row0 * ld_out + ch;
-        for (int t0 = a; t0 < b; t0 += SCAN_BATCH) {
+        const float* q = p + (size_t)a * ld;
+        OT* o = out + (size_t)(row0 + a) * ld_out + ch;
+        int t0 = a;
+        for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld, o += (size_t)SCAN_BATCH * ld_out) {
             float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH];
 #pragma unroll
             for (int k = 0; k < SCAN_BATCH; ++k) {
-                const bool in = t0 + k < b;
-                zl[k] = in ? p[(size_t)(t0 + k) * ld + z_off] : -INFINITY;
-                ul[k] = in ? p[(size_t)(t0 + k) * ld + u_off] : 0.f;
-                gl[k] = in ? p[(size_t)(t0 + k) * ld + g_off] : 0.f;
+                zl[k] = q[(size_t)k * ld + z_off];
+                ul[k] = q[(size_t)k * ld + u_off];
+                gl[k] = q[(size_t)k * ld + g_off];
             }
 #pragma unroll
             for (int k = 0; k < SCAN_BATCH; ++k) {
                 const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
                 S = fmaf(z, c - S, S);
-                if (t0 + k < b) ElemIO<OT>::store(o + (size_t)(t0 + k) * ld_out, S * out_gate_f<OT>(gl[k]));
+                ElemIO<OT>::store(o + (size_t)k * ld_out, S * out_gate_f<OT>(gl[k]));
+            }
+        }
+        if (t0 < b) {
+            float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH];
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {
+                const bool in = t0 + k < b;
+                zl[k] = in ? q[(size_t)k * ld + z_off] : -INFINITY;
+                ul[k] = in ? q[(size_t)k * ld + u_off] : 0.f;
+                gl[k] = in ? q[(size_t)k * ld + g_off] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < SCAN_BATCH; ++k) {
+                const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                S = fmaf(z, c - S, S);
+                if (t0 + k < b) ElemIO<OT>::store(o + (size_t)k * ld_out, S * out_gate_f<OT>(gl[k]));
             }
         }
         // the last run's warp ends at the sequence's last token of the step (an empty run: at the state it was handed)
