@@ -212,7 +212,7 @@ def test_gated_recurrence_keeps_a_far_token():
 
 
 @pytest.mark.parametrize("E,n_id,top,count,keep", [(6, 2, 3, 4, 2), (5, 1, 2, 3, 1), (4, 0, 1, 1, 1), (0, 3, 2, 1, 1), (3, 3, 2, 3, 2),
-                                                   (60, 4, 6, 8, 3), (7, 2, 2, 3, 3)])
+                                                   (60, 4, 6, 8, 3), (7, 2, 2, 3, 3), (100, 4, 5, 8, 4), (250, 6, 8, 16, 5)])      # (1, 2, 4 and 16 logits a lane)
 def test_router_by_scores(E, n_id, top, count, keep):
     from vlrf_b200.csrc import ops
     n_out = E + n_id

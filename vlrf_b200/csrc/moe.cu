@@ -78,14 +78,16 @@ moe_route_kernel(const float* __restrict__ z, int ld_z, int E, int top, int shar
     if (shared_gate && lane == 0) gate[t] = sigmoid_f(zr[E]);
 }
 
+// NI: logits a lane (the router's outputs are at most 32 · NI)
+template <int NI>
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, int groups, int keep, int n_identity, float scale,
                         const float* __restrict__ correction, const int* __restrict__ tok_slot, int* __restrict__ ids,
                         float* __restrict__ wts, int* __restrict__ rank, int* __restrict__ counts, int T) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
-    __shared__ float choice_sm[4][ROUTE_MAX_E];                // a warp's choice scores, then its groups' scores
-    __shared__ float group_sm[4][ROUTE_MAX_E];
+    __shared__ float choice_sm[4][NI * 32];                // a warp's choice scores, then its groups' scores
+    __shared__ float group_sm[4][NI * 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 4 + warp;
     if (t >= T) return;                                        // (whole warps leave; only warp barriers below)
@@ -94,10 +96,10 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
         return;
     }
     const float* zr = z + (size_t)t * ld_z;
-    float s[ROUTE_MAX_E / 32], v[ROUTE_MAX_E / 32];
+    float s[NI], v[NI];
     float m = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int e = i * 32 + lane;
         const float x = e < E ? zr[e] : -INFINITY;
         s[i] = (x == x) ? x : -INFINITY;                       // a NaN counts as no score at all
@@ -106,7 +108,7 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
     m = warp_max(m);
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int e = i * 32 + lane;
         s[i] = e < E ? expf(s[i] - m) : 0.f;
         sum += s[i];
@@ -116,7 +118,7 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
     float* cs = choice_sm[warp];
     float* gs = group_sm[warp];
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int e = i * 32 + lane;
         s[i] *= inv;
         v[i] = e < E ? s[i] + correction[e] : -INFINITY;
@@ -151,7 +153,7 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
             __syncwarp();
         }
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+        for (int i = 0; i < NI; ++i) {
             const int e = i * 32 + lane;
             if (e < E) { const float x = gs[e / per]; if (x == x) v[i] = -INFINITY; }       // its group was not kept
         }
@@ -164,7 +166,7 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
         int idx = 0x7fffffff;
         float sb = 0.f;
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+        for (int i = 0; i < NI; ++i) {
             const int e = i * 32 + lane;
             if (e < E && !(taken >> i & 1u) && (idx == 0x7fffffff || v[i] > best)) { best = v[i]; idx = e; sb = s[i]; }
         }
@@ -253,7 +255,13 @@ extern "C" int vlrf_moe_route_scored(const float* z, int ld_z, int E, int top, i
     VLRF_REQUIRE(top > 0 && top <= 32 && top <= keep * (E / groups), "moe_route_scored: a token takes 1…min(32, %d) experts, not %d", keep * (E / groups), top);
     VLRF_REQUIRE(n_identity >= 0 && n_identity <= E && correction != nullptr, "moe_route_scored: bad arguments");
     if (T == 0) return VLRF_OK;
-    launch_chained(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), (size_t)(0), stream, z, ld_z, E, top, groups, keep, n_identity, scale, correction, tok_slot, ids, wts, rank, counts, T);
+    const dim3 grid((T + 3) / 4), block(128);
+#define VLRF_ROUTE_SCORED(NI) launch_chained(moe_route_scored_kernel<NI>, grid, block, (size_t)(0), stream, z, ld_z, E, top, groups, keep, n_identity, scale, correction, tok_slot, ids, wts, rank, counts, T)
+    if (E <= 32) VLRF_ROUTE_SCORED(1);
+    else if (E <= 64) VLRF_ROUTE_SCORED(2);
+    else if (E <= 128) VLRF_ROUTE_SCORED(4);
+    else VLRF_ROUTE_SCORED(ROUTE_MAX_E / 32);
+#undef VLRF_ROUTE_SCORED
     return vlrf_check_launch("moe_route_scored");
 }
 
