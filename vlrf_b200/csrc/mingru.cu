@@ -9,12 +9,13 @@
 //
 //   mingru_step_kernel   steps of one token a sequence: a thread per (row, channel)
 //   mingru_scan_kernel   prompt steps: a lane per channel, 32 channels a CTA; the warps of the CTAs of a cluster (1 to 8
-//                        CTAs a sequence: as many as fill the GPU while a run keeps two batches of tokens) cut the sequence's
+//                        CTAs a sequence: as many as fill the GPU while a run keeps four batches of tokens) cut the sequence's
 //                        tokens of the step into consecutive runs.  Since S ← (1 − z) S + z c is linear in S, a run is the
 //                        map S ↦ A · S + B with A = Π (1 − z): each warp first forms (A, B) of its run; a CTA chains its
 //                        runs' maps in shared memory, the CTAs read one another's totals from there after a cluster
 //                        barrier; each warp then walks its run again from the state it begins with, writing the outputs.
-//                        The second walk finds its inputs in L2.
+//                        The second walk finds its inputs in L2.  Loads come in batches of 8 tokens; where runs are
+//                        long, a batch's loads are asked for ahead of the arithmetic on the batch before.
 #include "common.cuh"
 
 namespace {
@@ -60,8 +61,10 @@ mingru_step_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     ElemIO<OT>::store(out + (size_t)row * ld_out + ch, S * out_gate_f<OT>(g));
 }
 
-template <typename OT>
-__global__ void __launch_bounds__(SCAN_WARPS * 32)
+// PIPE: the loads of a full batch are asked for ahead of the arithmetic on the batch before (two sets of registers:
+// two CTAs an SM instead of three), for runs of several batches
+template <typename OT, bool PIPE>
+__global__ void __launch_bounds__(SCAN_WARPS * 32, PIPE ? 2 : (sizeof(OT) == 2 ? 3 : 1))
 mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off, int g_off, int W, float* state,
                    const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                    OT* __restrict__ out, int ld_out) {
@@ -86,18 +89,50 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
     if (live) {
         const float* q = p + (size_t)a * ld;                   // the run's next token
         int t0 = a;
-        for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld) {
-            float zl[SCAN_BATCH], ul[SCAN_BATCH];
+        if constexpr (PIPE) {
+            if (t0 + SCAN_BATCH <= b) {                            // full batches: the next one's loads ahead of this one's arithmetic
+                float zl[SCAN_BATCH], ul[SCAN_BATCH], zn[SCAN_BATCH], un[SCAN_BATCH];
 #pragma unroll
-            for (int k = 0; k < SCAN_BATCH; ++k) {
-                zl[k] = q[(size_t)k * ld + z_off];
-                ul[k] = q[(size_t)k * ld + u_off];
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    zl[k] = q[(size_t)k * ld + z_off];
+                    ul[k] = q[(size_t)k * ld + u_off];
+                }
+                for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH) {
+                    q += (size_t)SCAN_BATCH * ld;
+                    const bool more = t0 + 2 * SCAN_BATCH <= b;
+                    if (more) {
+#pragma unroll
+                        for (int k = 0; k < SCAN_BATCH; ++k) {
+                            zn[k] = q[(size_t)k * ld + z_off];
+                            un[k] = q[(size_t)k * ld + u_off];
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < SCAN_BATCH; ++k) {
+                        const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                        A *= 1.f - z;
+                        B = fmaf(z, c - B, B);
+                    }
+                    if (more) {
+#pragma unroll
+                        for (int k = 0; k < SCAN_BATCH; ++k) { zl[k] = zn[k]; ul[k] = un[k]; }
+                    }
+                }
             }
+        } else {
+            for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld) {
+                float zl[SCAN_BATCH], ul[SCAN_BATCH];
 #pragma unroll
-            for (int k = 0; k < SCAN_BATCH; ++k) {
-                const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
-                A *= 1.f - z;
-                B = fmaf(z, c - B, B);
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    zl[k] = q[(size_t)k * ld + z_off];
+                    ul[k] = q[(size_t)k * ld + u_off];
+                }
+#pragma unroll
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                    A *= 1.f - z;
+                    B = fmaf(z, c - B, B);
+                }
             }
         }
         if (t0 < b) {                                          // the run's last tokens, fewer than a batch
@@ -144,19 +179,53 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int z_off, int u_off,
         const float* q = p + (size_t)a * ld;
         OT* o = out + (size_t)(row0 + a) * ld_out + ch;
         int t0 = a;
-        for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld, o += (size_t)SCAN_BATCH * ld_out) {
-            float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH];
+        if constexpr (PIPE) {
+            if (t0 + SCAN_BATCH <= b) {
+                float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH], zn[SCAN_BATCH], un[SCAN_BATCH], gn[SCAN_BATCH];
 #pragma unroll
-            for (int k = 0; k < SCAN_BATCH; ++k) {
-                zl[k] = q[(size_t)k * ld + z_off];
-                ul[k] = q[(size_t)k * ld + u_off];
-                gl[k] = q[(size_t)k * ld + g_off];
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    zl[k] = q[(size_t)k * ld + z_off];
+                    ul[k] = q[(size_t)k * ld + u_off];
+                    gl[k] = q[(size_t)k * ld + g_off];
+                }
+                for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, o += (size_t)SCAN_BATCH * ld_out) {
+                    q += (size_t)SCAN_BATCH * ld;
+                    const bool more = t0 + 2 * SCAN_BATCH <= b;
+                    if (more) {
+#pragma unroll
+                        for (int k = 0; k < SCAN_BATCH; ++k) {
+                            zn[k] = q[(size_t)k * ld + z_off];
+                            un[k] = q[(size_t)k * ld + u_off];
+                            gn[k] = q[(size_t)k * ld + g_off];
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < SCAN_BATCH; ++k) {
+                        const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                        S = fmaf(z, c - S, S);
+                        ElemIO<OT>::store(o + (size_t)k * ld_out, S * out_gate_f<OT>(gl[k]));
+                    }
+                    if (more) {
+#pragma unroll
+                        for (int k = 0; k < SCAN_BATCH; ++k) { zl[k] = zn[k]; ul[k] = un[k]; gl[k] = gn[k]; }
+                    }
+                }
             }
+        } else {
+            for (; t0 + SCAN_BATCH <= b; t0 += SCAN_BATCH, q += (size_t)SCAN_BATCH * ld, o += (size_t)SCAN_BATCH * ld_out) {
+                float zl[SCAN_BATCH], ul[SCAN_BATCH], gl[SCAN_BATCH];
 #pragma unroll
-            for (int k = 0; k < SCAN_BATCH; ++k) {
-                const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
-                S = fmaf(z, c - S, S);
-                ElemIO<OT>::store(o + (size_t)k * ld_out, S * out_gate_f<OT>(gl[k]));
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    zl[k] = q[(size_t)k * ld + z_off];
+                    ul[k] = q[(size_t)k * ld + u_off];
+                    gl[k] = q[(size_t)k * ld + g_off];
+                }
+#pragma unroll
+                for (int k = 0; k < SCAN_BATCH; ++k) {
+                    const float z = Gate<OT>::sigmoid(zl[k]), c = candidate_f<OT>(ul[k]);
+                    S = fmaf(z, c - S, S);
+                    ElemIO<OT>::store(o + (size_t)k * ld_out, S * out_gate_f<OT>(gl[k]));
+                }
             }
         }
         if (t0 < b) {
@@ -208,15 +277,16 @@ extern "C" int vlrf_mingru_scan(const float* proj, int ld, int z_off, int u_off,
             launch_chained(mingru_step_kernel<__nv_bfloat16>, grid, dim3(256), (size_t)0, stream, proj, ld, z_off, u_off, g_off, W, state, seq_slot, seq_start, seq_pos0, n_seqs, (__nv_bfloat16*)out, ld_out);
     } else {
         VLRF_REQUIRE(n_seqs <= 65535, "mingru_scan: at most 65535 sequences a step, not %d", n_seqs);
-        // CTAs a sequence: doubled while the grid leaves SMs empty and a warp's run keeps two batches of tokens
+        // CTAs a sequence: doubled while the grid leaves SMs empty and a warp's run would still keep four batches of tokens
         const int base = ((W + 31) / 32) * n_seqs;
         int n_cta = 1;
-        while (n_cta < SCAN_MAX_CTAS && base * n_cta < scan_sm_count() && max_new >= 2 * n_cta * SCAN_WARPS * SCAN_BATCH) n_cta *= 2;
+        while (n_cta < SCAN_MAX_CTAS && base * n_cta < scan_sm_count() && max_new >= 8 * n_cta * SCAN_WARPS * SCAN_BATCH) n_cta *= 2;
+        const bool pipe = max_new >= 4 * n_cta * SCAN_WARPS * SCAN_BATCH;      // the longest sequence's runs have four batches
         const dim3 grid((unsigned)((W + 31) / 32), (unsigned)n_seqs, (unsigned)n_cta), cluster(1, 1, (unsigned)n_cta);
-        if (out_dtype == VLRF_F32)
-            launch_chained_cluster(mingru_scan_kernel<float>, grid, dim3(SCAN_WARPS * 32), (size_t)0, cluster, stream, proj, ld, z_off, u_off, g_off, W, state, seq_slot, seq_start, seq_pos0, (float*)out, ld_out);
-        else
-            launch_chained_cluster(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(SCAN_WARPS * 32), (size_t)0, cluster, stream, proj, ld, z_off, u_off, g_off, W, state, seq_slot, seq_start, seq_pos0, (__nv_bfloat16*)out, ld_out);
+#define VLRF_SCAN(OT, PIPE) launch_chained_cluster(mingru_scan_kernel<OT, PIPE>, grid, dim3(SCAN_WARPS * 32), (size_t)0, cluster, stream, proj, ld, z_off, u_off, g_off, W, state, seq_slot, seq_start, seq_pos0, (OT*)out, ld_out)
+        if (out_dtype == VLRF_F32) { if (pipe) VLRF_SCAN(float, true); else VLRF_SCAN(float, false); }
+        else { if (pipe) VLRF_SCAN(__nv_bfloat16, true); else VLRF_SCAN(__nv_bfloat16, false); }
+#undef VLRF_SCAN
     }
     return vlrf_check_launch("mingru_scan");
 }
