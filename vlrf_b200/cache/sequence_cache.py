@@ -3,7 +3,8 @@
 A sequence holds one *slot* from its first step to its end.  What a layer keeps per sequence is said
 by its mixer as a *need*:
 
-  KVNeed     keys and values per token: all of them (kind "full") or the last `window` (kind "window")
+  KVNeed     keys and values per token: all of them (kind "full") or the last `window` (kind "window"), with the
+             first `keep_first` of the sequence besides where a mixer says so
   LatentNeed one row of `width` numbers per token (a latent from which a mixer derives every head's keys and
              values, with whatever else it keeps per token in the same row): all of them, or the last `window`
   StateNeed  a state of fixed size per sequence (for mixers that carry one)
@@ -43,6 +44,7 @@ class KVNeed:
     kind: str = "full"      # "full" | "window"
     window: int = 0         # for kind "window": a query sees the last `window` keys, itself included
     v_dim: int = 0          # size of a value where it differs from the keys' head_dim (0: the same)
+    keep_first: int = 0     # for kind "window": the keys at positions below this stay visible whatever the window
 
 
 @dataclasses.dataclass(frozen=True)
@@ -123,7 +125,12 @@ class _KVGroup:
             first = max(0, cur_len + 1 - self.need.window) // BLOCK_TOKENS  # oldest key the first query sees
         last = (new_len + BLOCK_TOKENS - 1) // BLOCK_TOKENS
         row = self.table_host[slot]
+        # (the blocks of the kept first tokens are taken while the sequence passes them and never given back)
         return [i for i in range(first, last) if row[i] < 0]
+
+    def kept_blocks(self) -> int:
+        """Blocks at a sequence's start that stay whatever the window."""
+        return (getattr(self.need, "keep_first", 0) + BLOCK_TOKENS - 1) // BLOCK_TOKENS
 
 
 class _StateGroup:
@@ -169,6 +176,8 @@ class SequenceCache:
                     raise CacheError("a latent need keeps at least one number per token")
                 if need.kind == "window" and need.window <= 0:
                     raise CacheError("a window need has a positive window")
+                if getattr(need, "keep_first", 0) < 0 or (getattr(need, "keep_first", 0) and need.kind != "window"):
+                    raise CacheError("kept first tokens belong to a window need and are not negative")
                 g = _KVGroup(need, entries, self.n_blocks, self.n_slots, self.max_blocks, dtype, self.device)
             elif isinstance(need, StateNeed):
                 g = _StateGroup(need, entries, self.n_slots, self.device)
@@ -214,7 +223,7 @@ class SequenceCache:
                 for s in slots:
                     n = self.lengths[s]
                     if g.need.kind == "window":
-                        n = min(n, g.need.window)
+                        n = min(n, g.need.window + getattr(g.need, "keep_first", 0))
                     total += n * per_tok
         return total
 
@@ -262,10 +271,11 @@ class SequenceCache:
                 # blocks wholly before the window of the next query go back to the pool
                 keep_from = max(0, new_len + 1 - g.need.window) // BLOCK_TOKENS
                 row = g.table_host[slot]
-                old = [int(row[i]) for i in range(keep_from) if row[i] >= 0]
+                kept = g.kept_blocks()              # the blocks of the first tokens that stay visible
+                old = [int(row[i]) for i in range(kept, keep_from) if row[i] >= 0]
                 if old:
                     g.before_write()
-                    row[:keep_from] = -1
+                    row[kept:keep_from] = -1
                     g.pool.give(old)
 
     def release(self, slot: int) -> None:

@@ -105,6 +105,20 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p],
     "vlrf_attn_window": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_qkv_norm_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                  _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_int, _c_void_p, _c_void_p, _c_float, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_attn_window_ex": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float, _c_float, _c_int, _c_void_p,
+                            _c_void_p, _c_void_p],
+    "vlrf_attn_window_mma_ex": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float,
+                                _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "vlrf_embed_bigram": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "vlrf_scale_values": [_c_void_p, ctypes.c_longlong, _c_float, _c_void_p],
+    "vlrf_gate_mul_clamped": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                              _c_float, _c_void_p],
     "vlrf_attn_window_mma_takes": [_c_int] * 7,
     "vlrf_attn_window_mma": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                              _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float,
@@ -138,7 +152,7 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p],
     "vlrf_moe_route": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_void_p],
-    "vlrf_moe_route_scored": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p,
+    "vlrf_moe_route_scored": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "vlrf_moe_plan": [_c_void_p, _c_void_p, _c_int, _c_void_p],
     "vlrf_moe_gather": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,

@@ -10,10 +10,19 @@
 //   becomes (a cos t − b sin t, b cos t + a sin t) with t = position · freq[i] (float32; freq holds whatever scaling
 //   of the frequencies the model asks for).  Queries go to a matrix of their own in the activation dtype, keys and
 //   values into the cache at (slot, position).
+// qkv_norm_rope_append: the same with what some designs put between the product and the rotation, each a parameter:
+//   an RMS norm of queries and of keys (norm 1: every head by itself, one weight vector of dk entries shared by the
+//   heads; norm 2: all heads of the projection as one row, weights of H·dk and Hkv·dk entries; x / sqrt(mean(x²) + eps)
+//   · w in float32), the pairing of rotated entries (pairing 1: entry 2i with entry 2i + 1), a factor on every cosine
+//   and sine (`magnitude`), and values that are the keys as projected (v_off = k_off: they are read before norm and
+//   rotation).  A layer that reads another layer's cache has no key or value columns (write_cache 0).
 // attn_window: one warp per (token, head) walks the visible keys of the token's slot in chunks of 32 with an online
 //   softmax in float32; any mix of prompt tokens and single tokens.  Every size (dk, dv ≤ 256) is taken; the 32-bit
 //   path's attention, and the fallback of the bfloat16 path.  The result is multiplied by out_scale (a mixer that
 //   sums several branches puts a branch's weight there) and written at a column offset of wider rows.
+//   Further parameters (attn_window_ex): softcap c > 0 squashes every score to c · tanh(score / c) after the scale;
+//   keep_first n > 0 lets every query also see the keys at positions below n, whatever the window (they keep their
+//   positions); sink (one float32 a query head) adds exp(sink_h) to the softmax's denominator, with no key and no value.
 #include "common.cuh"
 
 namespace {
@@ -26,7 +35,8 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
                        int rot, ET* __restrict__ q_out, int ldq, ET* __restrict__ Kc, ET* __restrict__ Vc,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                        const int* __restrict__ tok_pos, int H, int Hkv, int dk, int dv, int BT, int write_cache,
-                       int* __restrict__ dev_err) {
+                       int norm, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int pairing,
+                       float magnitude, int* __restrict__ dev_err) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -35,18 +45,65 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
     const int pos = tok_pos[t];
     const float* row = proj + (size_t)t * ld;
     const int half = rot / 2;
-    // the token's cosines and sines once, for all heads: [half] each
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the token's cosines and sines once, for all heads: [half] each; then 1 / rms of every normed head: [H + Hkv]
     extern __shared__ float cs_sm[];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freq[i], &cs_sm[half + i], &cs_sm[i]);
+    float* inv_sm = cs_sm + rot;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cn;
+        sincosf((float)pos * freq[i], &sn, &cn);
+        cs_sm[i] = cn * magnitude;
+        cs_sm[half + i] = sn * magnitude;
+    }
+    const int n_kh = write_cache ? Hkv : 0;
+    if (norm == 1) {
+        for (int h = warp; h < H + n_kh; h += 4) {
+            const float* head = h < H ? row + q_off + h * dk : row + k_off + (h - H) * dk;
+            float ss = 0.f;
+            for (int c = lane; c < dk; c += 32) ss = fmaf(head[c], head[c], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) inv_sm[h] = 1.f / sqrtf(ss / (float)dk + eps);
+        }
+    } else if (norm == 2) {
+        __shared__ float red[2][4];
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < H * dk; i += blockDim.x) sq = fmaf(row[q_off + i], row[q_off + i], sq);
+        for (int i = threadIdx.x; i < n_kh * dk; i += blockDim.x) sk = fmaf(row[k_off + i], row[k_off + i], sk);
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+        __syncthreads();
+        if (threadIdx.x < H + n_kh) {
+            const bool isq = (int)threadIdx.x < H;
+            const float tot = red[isq ? 0 : 1][0] + red[isq ? 0 : 1][1] + red[isq ? 0 : 1][2] + red[isq ? 0 : 1][3];
+            inv_sm[threadIdx.x] = 1.f / sqrtf(tot / (float)((isq ? H : Hkv) * dk) + eps);
+        }
+        for (int h = threadIdx.x + 128; h < H + n_kh; h += 128) {          // (more heads than threads)
+            const bool isq = h < H;
+            const float tot = red[isq ? 0 : 1][0] + red[isq ? 0 : 1][1] + red[isq ? 0 : 1][2] + red[isq ? 0 : 1][3];
+            inv_sm[h] = 1.f / sqrtf(tot / (float)((isq ? H : Hkv) * dk) + eps);
+        }
+    }
     __syncthreads();
-    auto rotated = [&](const float* head, int c) -> float {
-        if (c >= rot) return head[c];
-        if (c < half) return head[c] * cs_sm[c] - head[c + half] * cs_sm[half + c];
-        return head[c] * cs_sm[c - half] + head[c - half] * cs_sm[c];
+    // entry c of a head after the norm: w points at the head's weights (norm 1: the shared vector; norm 2: its own part)
+    auto normed = [&](const float* head, const float* w, float inv, int c) -> float {
+        return norm ? head[c] * inv * w[c] : head[c];
+    };
+    auto rotated = [&](const float* head, const float* w, float inv, int c) -> float {
+        const float x = normed(head, w, inv, c);
+        if (c >= rot) return x;
+        if (pairing == 1) {                                   // entry 2i with entry 2i + 1
+            const int i = c >> 1;
+            const float y = normed(head, w, inv, c ^ 1);
+            return (c & 1) ? x * cs_sm[i] + y * cs_sm[half + i] : x * cs_sm[i] - y * cs_sm[half + i];
+        }
+        if (c < half) return x * cs_sm[c] - normed(head, w, inv, c + half) * cs_sm[half + c];
+        return x * cs_sm[c - half] + normed(head, w, inv, c - half) * cs_sm[c];
     };
     for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
         const int h = i / dk, c = i - h * dk;
-        ElemIO<ET>::store(q_out + (size_t)t * ldq + i, rotated(row + q_off + h * dk, c));
+        const float* w = norm == 2 ? q_norm + h * dk : q_norm;
+        ElemIO<ET>::store(q_out + (size_t)t * ldq + i, rotated(row + q_off + h * dk, w, norm ? inv_sm[h] : 1.f, c));
     }
     if (!write_cache) return;
     const int bi = pos / BT;
@@ -57,7 +114,9 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
     }
     for (int i = threadIdx.x; i < Hkv * dk; i += blockDim.x) {
         const int h = i / dk, c = i - h * dk;
-        ElemIO<ET>::store(Kc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dk + c, rotated(row + k_off + h * dk, c));
+        const float* w = norm == 2 ? k_norm + h * dk : k_norm;
+        ElemIO<ET>::store(Kc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dk + c,
+                          rotated(row + k_off + h * dk, w, norm ? inv_sm[H + h] : 1.f, c));
     }
     for (int i = threadIdx.x; i < Hkv * dv; i += blockDim.x) {
         const int h = i / dv, c = i - h * dv;
@@ -70,7 +129,8 @@ __global__ void __launch_bounds__(AW_WARPS * 32)
 attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ Kc, const ET* __restrict__ Vc,
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                    const int* __restrict__ tok_pos, ET* __restrict__ out, int ld_out, int H, int Hkv, int dk, int dv, int BT,
-                   float scale, int window, float out_scale, int* __restrict__ dev_err) {
+                   float scale, int window, float out_scale, float softcap, int keep_first, const float* __restrict__ sink,
+                   int* __restrict__ dev_err) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float q_sm[];  // [AW_WARPS][dk]
@@ -94,19 +154,23 @@ attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ 
     const int* table = block_table + (size_t)slot * max_blocks;
     bool lost = false;
 
-    for (int k0 = (first / 32) * 32; k0 <= pos; k0 += 32) {
+    // the keys kept whatever the window (positions below keep_first that the window no longer reaches), then the window
+    const int n_kept = (window > 0 && keep_first > 0) ? min(keep_first, first) : 0;
+    const int kept_end = ((n_kept + 31) / 32) * 32, win_begin = (first / 32) * 32;
+    for (int k0 = n_kept > 0 ? 0 : win_begin; k0 <= pos; k0 += 32) {
+        if (k0 >= kept_end && k0 < win_begin) { k0 = win_begin - 32; continue; }   // (the chunks between the two ranges)
         const int blk = table[k0 / BT];
         if (blk < 0) { lost = true; break; }
         const size_t kbase = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * dk;
         const size_t vbase = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * dv;
         const int key = k0 + lane;
-        const bool valid = key >= first && key <= pos;
+        const bool valid = (key >= first || key < n_kept) && key <= pos;
         float s = -INFINITY;
         if (valid) {
             const ET* krow = Kc + kbase + (size_t)lane * dk;
             float dot = 0.f;
             for (int c = 0; c < dk; ++c) dot = fmaf(q[c], ElemIO<ET>::load(krow + c), dot);
-            s = dot;
+            s = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
         }
         const float m_new = fmaxf(m, warp_max(s));      // at least one key of the chunk is valid
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -128,6 +192,13 @@ attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ 
         m = m_new;
     }
     if (lost && lane == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+    if (sink != nullptr) {                               // exp(sink) joins the denominator: no key, no value
+        const float sk = sink[h], m_new = fmaxf(m, sk);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < AW_MAX / 32; ++i) acc[i] *= corr;
+    }
     const float inv = (l > 0.f) ? out_scale / l : 0.f;
     ET* dst = out + (size_t)t * ld_out + (size_t)h * dv;
 #pragma unroll
@@ -138,39 +209,56 @@ attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ 
 }
 }  // namespace
 
-extern "C" int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_off, int v_off, const float* freq, int rot,
-                                    void* q_out, int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks,
-                                    const int* tok_slot, const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT,
-                                    int write_cache, int* dev_err, cudaStream_t stream) {
+extern "C" int vlrf_qkv_norm_rope_append(const float* proj, int ld, int q_off, int k_off, int v_off, const float* freq, int rot,
+                                         void* q_out, int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks,
+                                         const int* tok_slot, const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT,
+                                         int write_cache, int norm, const float* q_norm, const float* k_norm, float eps, int pairing,
+                                         float magnitude, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && H > 0 && Hkv > 0 && dk > 0 && dv > 0 && BT > 0 && max_blocks > 0, "qkv_rope_append: bad sizes");
     VLRF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dk, "qkv_rope_append: %d rotated entries of a head of %d", rot, dk);
     VLRF_REQUIRE(rot == 0 || freq != nullptr, "qkv_rope_append: a rotation needs its frequencies");
-    VLRF_REQUIRE(q_off + H * dk <= ld && k_off + Hkv * dk <= ld && v_off + Hkv * dv <= ld && ldq >= H * dk,
-                 "qkv_rope_append: columns lie outside the row");
+    VLRF_REQUIRE(q_off >= 0 && q_off + H * dk <= ld && ldq >= H * dk, "qkv_rope_append: columns lie outside the row");
+    VLRF_REQUIRE(!write_cache || (k_off >= 0 && v_off >= 0 && k_off + Hkv * dk <= ld && v_off + Hkv * dv <= ld && Kc != nullptr && Vc != nullptr),
+                 "qkv_rope_append: key or value columns lie outside the row");
+    VLRF_REQUIRE(norm >= 0 && norm <= 2 && (norm == 0 || (q_norm != nullptr && (k_norm != nullptr || !write_cache) && eps > 0.f)),
+                 "qkv_rope_append: a norm of queries and keys needs its weights and a positive eps");
+    VLRF_REQUIRE(pairing == 0 || pairing == 1, "qkv_rope_append: rotated entries pair by halves (0) or as neighbours (1)");
     VLRF_REQUIRE(dev_err != nullptr, "qkv_rope_append: needs the device error word");
     if (T == 0) return VLRF_OK;
+    const size_t smem = (size_t)(rot + H + Hkv) * sizeof(float);
+    VLRF_REQUIRE(smem <= 48 * 1024, "qkv_rope_append: %d heads are more than the kernel's shared memory takes", H + Hkv);
     if (dtype == VLRF_F32)
-        launch_chained(qkv_rope_append_kernel<float>, dim3(T), dim3(128), (size_t)rot * sizeof(float), stream, proj, ld, q_off, k_off, v_off, freq, rot,
+        launch_chained(qkv_rope_append_kernel<float>, dim3(T), dim3(128), smem, stream, proj, ld, q_off, k_off, v_off, freq, rot,
                        (float*)q_out, ldq, (float*)Kc, (float*)Vc, block_table, max_blocks, tok_slot, tok_pos, H, Hkv, dk, dv, BT,
-                       write_cache, dev_err);
+                       write_cache, norm, q_norm, k_norm, eps, pairing, magnitude, dev_err);
     else if (dtype == VLRF_BF16)
-        launch_chained(qkv_rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)rot * sizeof(float), stream, proj, ld, q_off, k_off, v_off, freq,
+        launch_chained(qkv_rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(128), smem, stream, proj, ld, q_off, k_off, v_off, freq,
                        rot, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)Kc, (__nv_bfloat16*)Vc, block_table, max_blocks, tok_slot,
-                       tok_pos, H, Hkv, dk, dv, BT, write_cache, dev_err);
+                       tok_pos, H, Hkv, dk, dv, BT, write_cache, norm, q_norm, k_norm, eps, pairing, magnitude, dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "qkv_rope_append: unknown dtype %d", dtype);
     return vlrf_check_launch("qkv_rope_append");
 }
 
-extern "C" int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table,
-                                int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H,
-                                int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale, int* dev_err,
-                                cudaStream_t stream) {
+extern "C" int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_off, int v_off, const float* freq, int rot,
+                                    void* q_out, int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks,
+                                    const int* tok_slot, const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT,
+                                    int write_cache, int* dev_err, cudaStream_t stream) {
+    VLRF_REQUIRE(k_off + Hkv * dk <= ld && v_off + Hkv * dv <= ld, "qkv_rope_append: columns lie outside the row");
+    return vlrf_qkv_norm_rope_append(proj, ld, q_off, k_off, v_off, freq, rot, q_out, ldq, Kc, Vc, dtype, block_table, max_blocks,
+                                     tok_slot, tok_pos, T, H, Hkv, dk, dv, BT, write_cache, 0, nullptr, nullptr, 0.f, 0, 1.f, dev_err,
+                                     stream);
+}
+
+extern "C" int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table,
+                                   int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H,
+                                   int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale, float softcap,
+                                   int keep_first, const float* sink, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && H > 0 && Hkv > 0 && max_blocks > 0, "attn_window: bad sizes");
     VLRF_REQUIRE(H % Hkv == 0, "attn_window: %d heads cannot share %d key/value heads", H, Hkv);
     VLRF_REQUIRE(dk > 0 && dk <= AW_MAX && dv > 0 && dv <= AW_MAX, "attn_window: head sizes %d and %d are not in 1…%d", dk, dv, AW_MAX);
     VLRF_REQUIRE(BT % 32 == 0, "attn_window: cache blocks of %d tokens are not a multiple of 32", BT);
-    VLRF_REQUIRE(window >= 0, "attn_window: negative window");
+    VLRF_REQUIRE(window >= 0 && keep_first >= 0 && softcap >= 0.f, "attn_window: negative window, kept tokens or cap");
     VLRF_REQUIRE(ldq >= H * dk && ld_out >= H * dv, "attn_window: leading sizes are smaller than the rows");
     VLRF_REQUIRE(dev_err != nullptr, "attn_window: needs the device error word");
     if (T == 0) return VLRF_OK;
@@ -179,12 +267,20 @@ extern "C" int vlrf_attn_window(const void* q, int dtype, int ldq, const void* K
     if (dtype == VLRF_F32)
         launch_chained(attn_window_kernel<float>, grid, dim3(AW_WARPS * 32), smem, stream, (const float*)q, ldq, (const float*)Kc,
                        (const float*)Vc, block_table, max_blocks, tok_slot, tok_pos, (float*)out, ld_out, H, Hkv, dk, dv, BT, scale,
-                       window, out_scale, dev_err);
+                       window, out_scale, softcap, keep_first, sink, dev_err);
     else if (dtype == VLRF_BF16)
         launch_chained(attn_window_kernel<__nv_bfloat16>, grid, dim3(AW_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq,
                        (const __nv_bfloat16*)Kc, (const __nv_bfloat16*)Vc, block_table, max_blocks, tok_slot, tok_pos,
-                       (__nv_bfloat16*)out, ld_out, H, Hkv, dk, dv, BT, scale, window, out_scale, dev_err);
+                       (__nv_bfloat16*)out, ld_out, H, Hkv, dk, dv, BT, scale, window, out_scale, softcap, keep_first, sink, dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "attn_window: unknown dtype %d", dtype);
     return vlrf_check_launch("attn_window");
+}
+
+extern "C" int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table,
+                                int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H,
+                                int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale, int* dev_err,
+                                cudaStream_t stream) {
+    return vlrf_attn_window_ex(q, dtype, ldq, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out, T, H, Hkv, dk, dv, BT,
+                               scale, window, out_scale, 0.f, 0, nullptr, dev_err, stream);
 }

@@ -13,6 +13,11 @@
 // A decode step may cut every context into `n_split` parts (CTA x = part; part p takes the key tiles p, p + n_split, …);
 // the parts leave unnormalised sums with their maximum and denominator in `partials`, and a second kernel merges them in
 // a fixed order.  The result is multiplied by out_scale.
+//
+// Parameters beside the window: softcap c > 0 squashes every scaled score to c · tanh(score / c); keep_first n > 0 lets
+// every query also see the keys at positions below n (the tiles that hold them come first in a CTA's list of tiles,
+// ahead of the window's); sink (a float32 per query head) adds exp(sink_h) to the softmax's denominator where the parts
+// of a row are complete (in the kernel, or in the merge of a cut context).
 #include "common.cuh"
 
 namespace {
@@ -54,7 +59,8 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                        const __nv_bfloat16* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                        __nv_bfloat16* __restrict__ out, int ld_out, float* __restrict__ partials, int H, int Hkv, int dk, int dv,
-                       float scale, int window, float out_scale, int n_split, int* __restrict__ dev_err) {
+                       float scale, int window, float out_scale, int n_split, float softcap, int keep_first,
+                       const float* __restrict__ sink, int* __restrict__ dev_err) {
     constexpr int KS = DKP + 8, VS = DVP + 8;       // row strides in elements: 16 bytes of padding keep ldmatrix off bank conflicts
     constexpr int WKEYS = DEC ? WM_BK / WM_WARPS : WM_BK;      // keys of a tile that one warp takes
     constexpr int NT_S = WKEYS / 8, NT_O = DVP / 8, KS_QK = DKP / 16, KS_PV = WKEYS / 16;
@@ -78,13 +84,17 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
     const int n_tok = min(TPT, n_new - qt * TPT);   // tokens of this tile
     const int q_first = pos0 + qt * TPT, q_last = q_first + n_tok - 1;
     const int kt_first = (window > 0) ? max(0, q_first - window + 1) / WM_BK : 0;
-    const int n_kt_all = q_last / WM_BK - kt_first + 1;
+    // tiles of kept first keys that the window's tiles do not cover come first in the list: list entry j is tile j for
+    // j < n_keep_t, else tile kt_first + j − n_keep_t
+    const int n_keep_t = (window > 0 && keep_first > 0) ? min(kt_first, (keep_first + WM_BK - 1) / WM_BK) : 0;
+    const int n_kt_all = n_keep_t + q_last / WM_BK - kt_first + 1;
     const int n_kt = (n_kt_all - part + n_split - 1) / n_split;                  // this part's tiles: part, part + n_split, …
+    auto tile_of = [&](int i) { const int j = part + i * n_split; return j < n_keep_t ? j : kt_first + j - n_keep_t; };
     const int* table = block_table + (size_t)slot * max_blocks;
     const int n_exist = pos0 + n_new;               // keys of the sequence that the cache holds
 
     auto load_kv = [&](int i) {                     // all threads: key/value tile number i of this CTA into stage i % NST
-        const int kt = kt_first + part + i * n_split;
+        const int kt = tile_of(i);
         const int blk = table[kt];
         __nv_bfloat16* kd = k_tiles + (i % NST) * WM_BK * KS;
         __nv_bfloat16* vd = v_tiles + (i % NST) * WM_BK * VS;
@@ -126,6 +136,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
     for (int j = 0; j < NT_O; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float sl2 = scale * 1.4426950408889634f;  // scores are kept in units of log2(e)
+    const float cap2 = softcap * 1.4426950408889634f, cap_in = softcap > 0.f ? 2.f / softcap : 0.f;   // (v · cap_in = 2 x log2e / c)
     const int lr[2] = {wrow + g, wrow + g + 8};                                  // this thread's two rows of the tile
     const int q_row[2] = {q_first + lr[0] / R, q_first + lr[1] / R};             // … and their positions
 
@@ -141,7 +152,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                 w_ldsm_x4(qb + ((wrow + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8) * 2, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
         }
         if (active) {
-            const int k_base = (kt_first + part + i * n_split) * WM_BK;
+            const int k_base = tile_of(i) * WM_BK;
             const uint32_t kb = wsm(k_tiles + (i % NST) * WM_BK * KS), vb = wsm(v_tiles + (i % NST) * WM_BK * VS);
             float s[NT_S][4];
 #pragma unroll
@@ -165,9 +176,11 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                 for (int e = 0; e < 4; ++e) {
                     const int r = e >> 1;
                     float v = s[j][e] * sl2;
+                    if (softcap > 0.f)      // c · tanh(x / c) = c · (1 − 2 / (2^(2x log2e / c) + 1)), in units of log2 e
+                        v = cap2 * (1.f - __fdividef(2.f, exp2f(v * cap_in) + 1.f));
                     if (need_mask) {
                         const int key = k_base + wkey + j * 8 + 2 * t + (e & 1);
-                        if (key > q_row[r] || (window > 0 && key <= q_row[r] - window)) v = -INFINITY;
+                        if (key > q_row[r] || (window > 0 && key <= q_row[r] - window && key >= keep_first)) v = -INFINITY;
                     }
                     s[j][e] = v;
                     m_new[r] = fmaxf(m_new[r], v);
@@ -244,6 +257,12 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
             }
             const int row = row0 + qt * TPT + row_l / R, h = hk * R + row_l % R;
             if (n_split == 1) {
+                if (sink != nullptr) {               // exp(sink) joins the denominator
+                    const float sk = sink[h] * 1.4426950408889634f, M2 = fmaxf(M, sk);
+                    const float f = (M == -INFINITY) ? 0.f : exp2f(M - M2);
+                    L = L * f + exp2f(sk - M2);
+                    acc *= f;
+                }
                 if (c < dv) out[(size_t)row * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * (out_scale / L) : 0.f);
             } else {
                 float* dst = partials + (((size_t)row * H + h) * n_split + part) * (dv + 2);
@@ -260,7 +279,13 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
         if (ti >= n_tok) continue;
         const int row = row0 + qt * TPT + ti, h = hk * R + lr[r] % R;
         if (n_split == 1) {
-            const float inv = (l_run[r] > 0.f) ? out_scale / l_run[r] : 0.f;
+            float fo = 1.f;
+            if (sink != nullptr) {                   // exp(sink) joins the denominator
+                const float sk = sink[h] * 1.4426950408889634f, M2 = fmaxf(m_run[r], sk);
+                fo = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - M2);
+                l_run[r] = l_run[r] * fo + exp2f(sk - M2);
+            }
+            const float inv = (l_run[r] > 0.f) ? fo * out_scale / l_run[r] : 0.f;
             __nv_bfloat16* dst = out + (size_t)row * ld_out + (size_t)h * dv + 2 * t;
 #pragma unroll
             for (int j = 0; j < NT_O; ++j)
@@ -279,7 +304,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
 // order of the parts.  A part that saw no key has l = 0.
 __global__ void __launch_bounds__(128)
 attn_window_merge_kernel(const float* __restrict__ partials, const int* __restrict__ seq_slot, __nv_bfloat16* __restrict__ out,
-                         int ld_out, int H, int dv, int n_split, float out_scale) {
+                         int ld_out, int H, int dv, int n_split, float out_scale, const float* __restrict__ sink) {
     pdl_wait();
     pdl_launch_dependents();
     const int row = blockIdx.x, h = blockIdx.y;
@@ -288,7 +313,9 @@ attn_window_merge_kernel(const float* __restrict__ partials, const int* __restri
     float M = -INFINITY;
     for (int s = 0; s < n_split; ++s)
         if (p[s * (dv + 2) + dv + 1] > 0.f) M = fmaxf(M, p[s * (dv + 2) + dv]);
-    float L = 0.f;
+    const float sk = sink != nullptr ? sink[h] * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sk);
+    float L = sink != nullptr ? exp2f(sk - M) : 0.f;
     for (int s = 0; s < n_split; ++s) {
         const float l = p[s * (dv + 2) + dv + 1];
         if (l > 0.f) L += l * exp2f(p[s * (dv + 2) + dv] - M);
@@ -306,7 +333,7 @@ template <int DKP, int DVP, bool DEC>
 int launch_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                       const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                       int n_seqs, int max_new, int H, int Hkv, int dk, int dv, float scale, int window, float out_scale, int n_split,
-                      int* dev_err, cudaStream_t stream) {
+                      float softcap, int keep_first, const float* sink, int* dev_err, cudaStream_t stream) {
     // stages of a decode step: as many as leave room for two or three CTAs an SM
     constexpr int NST = DEC ? (DKP + DVP <= 160 ? 4 : DKP + DVP <= 224 ? 3 : 2) : 2;
     const size_t smem = (size_t)((DEC ? 16 : 64) * (DKP + 8) + NST * 64 * (DKP + 8) + NST * 64 * (DVP + 8)) * 2;
@@ -321,7 +348,8 @@ int launch_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, co
     dim3 grid(((max_new + tpt - 1) / tpt) * n_split, Hkv, n_seqs);
     cudaError_t e = launch_chained(kern, grid, dim3(WM_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)Kc,
                                    (const __nv_bfloat16*)Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0,
-                                   (__nv_bfloat16*)out, ld_out, partials, H, Hkv, dk, dv, scale, window, out_scale, n_split, dev_err);
+                                   (__nv_bfloat16*)out, ld_out, partials, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap,
+                                   keep_first, sink, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_window_mma: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_window_mma");
 }
@@ -334,13 +362,15 @@ extern "C" int vlrf_attn_window_mma_takes(int H, int Hkv, int dk, int dv, int BT
             dv <= 128 && BT == WM_BK && ldq % 8 == 0 && ld_out % 2 == 0) ? 1 : 0;
 }
 
-extern "C" int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
-                                    const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
-                                    float* partials, int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale,
-                                    int window, float out_scale, int n_split, int* dev_err, cudaStream_t stream) {
+extern "C" int vlrf_attn_window_mma_ex(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                                       const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
+                                       float* partials, int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale,
+                                       int window, float out_scale, int n_split, float softcap, int keep_first, const float* sink,
+                                       int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_attn_window_mma_takes(H, Hkv, dk, dv, BT, ldq, ld_out), "attn_window_mma: heads %d/%d, sizes %d and %d, block %d are not taken",
                  H, Hkv, dk, dv, BT);
     VLRF_REQUIRE(n_seqs >= 0 && max_new >= 0 && max_blocks > 0 && window >= 0 && dev_err != nullptr, "attn_window_mma: bad arguments");
+    VLRF_REQUIRE(keep_first >= 0 && softcap >= 0.f, "attn_window_mma: negative kept tokens or cap");
     VLRF_REQUIRE(n_seqs <= 65535 && Hkv <= 65535, "attn_window_mma: too many sequences or heads for one launch");
     VLRF_REQUIRE(n_split >= 1 && (n_split == 1 || (max_new == 1 && partials != nullptr)),
                  "attn_window_mma: contexts are cut into parts in decode steps only, and the parts need scratch");
@@ -350,17 +380,26 @@ extern "C" int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, cons
     int st = VLRF_ERR_UNSUPPORTED;
     const bool dec = max_new == 1 && H / Hkv <= 16;            // every tile holds one token's heads: the warps deal the keys
 #define GO(A, B) if (kp == A && vp == B) st = dec ? launch_window_mma<A, B, true>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
-        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, dev_err, stream) \
+        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, dev_err, stream) \
         : launch_window_mma<A, B, false>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
-        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, dev_err, stream);
+        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, dev_err, stream);
     GO(32, 32) GO(32, 64) GO(32, 96) GO(32, 128) GO(64, 32) GO(64, 64) GO(64, 96) GO(64, 128)
     GO(96, 32) GO(96, 64) GO(96, 96) GO(96, 128) GO(128, 32) GO(128, 64) GO(128, 96) GO(128, 128)
 #undef GO
     if (st != VLRF_OK) return st;
     if (n_split > 1) {
         launch_chained(attn_window_merge_kernel, dim3(n_seqs, H), dim3(128), (size_t)0, stream, (const float*)partials, seq_slot,
-                       (__nv_bfloat16*)out, ld_out, H, dv, n_split, out_scale);
+                       (__nv_bfloat16*)out, ld_out, H, dv, n_split, out_scale, sink);
         return vlrf_check_launch("attn_window_merge");
     }
     return VLRF_OK;
+}
+
+extern "C" int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                                    const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
+                                    float* partials, int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale,
+                                    int window, float out_scale, int n_split, int* dev_err, cudaStream_t stream) {
+    return vlrf_attn_window_mma_ex(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, out, ld_out, partials,
+                                   n_seqs, max_new, H, Hkv, dk, dv, BT, scale, window, out_scale, n_split, 0.f, 0, nullptr, dev_err,
+                                   stream);
 }

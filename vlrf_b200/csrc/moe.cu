@@ -9,7 +9,8 @@
 //                only inside the `keep` groups (of `groups` equal groups of neighbouring experts) whose largest such
 //                score is largest; the weights are the chosen s · scale, not renormalized.  The last n_identity
 //                router outputs stand for experts that return their input: they get id −2, no rank and no row, and
-//                moe_combine adds weight · input for them.
+//                moe_combine adds weight · input for them.  With `scoring` 1 the scores are sigmoid(logit), each
+//                output by itself, instead of the softmax over all of them; everything else is the same.
 //   moe_plan     offsets[e] = rows of the experts before e (E + 1 entries); the counters are left zero.
 //   moe_gather   pair (token, j) gets row offsets[expert] + rank of the expert-sorted buffer: the token's input row
 //                is copied there and the row's number kept.
@@ -82,7 +83,7 @@ moe_route_kernel(const float* __restrict__ z, int ld_z, int E, int top, int shar
 template <int NI>
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, int groups, int keep, int n_identity, float scale,
-                        const float* __restrict__ correction, const int* __restrict__ tok_slot, int* __restrict__ ids,
+                        int scoring, const float* __restrict__ correction, const int* __restrict__ tok_slot, int* __restrict__ ids,
                         float* __restrict__ wts, int* __restrict__ rank, int* __restrict__ counts, int T) {
     pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
     pdl_launch_dependents();
@@ -110,11 +111,12 @@ moe_route_scored_kernel(const float* __restrict__ z, int ld_z, int E, int top, i
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
         const int e = i * 32 + lane;
-        s[i] = e < E ? expf(s[i] - m) : 0.f;
+        if (scoring == 1) s[i] = e < E ? 1.f / (1.f + expf(-s[i])) : 0.f;       // (a NaN logit became −∞: score 0)
+        else s[i] = e < E ? expf(s[i] - m) : 0.f;
         sum += s[i];
     }
     sum = warp_sum(sum);
-    const float inv = 1.f / sum;
+    const float inv = scoring == 1 ? 1.f : 1.f / sum;
     float* cs = choice_sm[warp];
     float* gs = group_sm[warp];
 #pragma unroll
@@ -248,15 +250,16 @@ extern "C" int vlrf_moe_route(const float* z, int ld_z, int E, int top, int shar
 }
 
 extern "C" int vlrf_moe_route_scored(const float* z, int ld_z, int E, int top, int groups, int keep, int n_identity, float scale,
-                                     const float* correction, const int* tok_slot, int* ids, float* wts, int* rank, int* counts,
+                                     int scoring, const float* correction, const int* tok_slot, int* ids, float* wts, int* rank, int* counts,
                                      int T, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && E > 0 && E <= ROUTE_MAX_E && ld_z >= E, "moe_route_scored: takes 1…%d router outputs, not %d", ROUTE_MAX_E, E);
     VLRF_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "moe_route_scored: %d outputs in %d groups of which %d are kept", E, groups, keep);
     VLRF_REQUIRE(top > 0 && top <= 32 && top <= keep * (E / groups), "moe_route_scored: a token takes 1…min(32, %d) experts, not %d", keep * (E / groups), top);
     VLRF_REQUIRE(n_identity >= 0 && n_identity <= E && correction != nullptr, "moe_route_scored: bad arguments");
+    VLRF_REQUIRE(scoring == 0 || scoring == 1, "moe_route_scored: scores are a softmax over all outputs (0) or sigmoids (1), not %d", scoring);
     if (T == 0) return VLRF_OK;
     const dim3 grid((T + 3) / 4), block(128);
-#define VLRF_ROUTE_SCORED(NI) launch_chained(moe_route_scored_kernel<NI>, grid, block, (size_t)(0), stream, z, ld_z, E, top, groups, keep, n_identity, scale, correction, tok_slot, ids, wts, rank, counts, T)
+#define VLRF_ROUTE_SCORED(NI) launch_chained(moe_route_scored_kernel<NI>, grid, block, (size_t)(0), stream, z, ld_z, E, top, groups, keep, n_identity, scale, scoring, correction, tok_slot, ids, wts, rank, counts, T)
     if (E <= 32) VLRF_ROUTE_SCORED(1);
     else if (E <= 64) VLRF_ROUTE_SCORED(2);
     else if (E <= 128) VLRF_ROUTE_SCORED(4);

@@ -27,7 +27,42 @@
 
 namespace {
 __device__ __forceinline__ float gate_f(int act, float g) {
-    return act == VLRF_ACT_SILU ? silu_f(g) : act == VLRF_ACT_SIGMOID ? sigmoid_f(g) : fmaxf(g, 0.f);
+    return act == VLRF_ACT_SILU ? silu_f(g) : act == VLRF_ACT_SIGMOID ? sigmoid_f(g) : act == VLRF_ACT_GELU_TANH ? gelu_tanh_f(g) : fmaxf(g, 0.f);
+}
+
+// A gate with bounds: g' = min(g, limit), u' = clamp(u, −limit, limit), out = g' · sigmoid(alpha · g') · (u' + 1).
+template <typename AT, typename BT, typename OT>
+__global__ void gate_mul_clamped_kernel(const AT* a, int lda, const BT* b, int ldb, OT* out, int ldo, int rows, int cols, float limit,
+                                        float alpha) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols) return;
+    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+    const float g = fminf(ElemIO<AT>::load(a + (size_t)r * lda + c), limit);
+    const float u = fminf(fmaxf(ElemIO<BT>::load(b + (size_t)r * ldb + c), -limit), limit);
+    ElemIO<OT>::store(out + (size_t)r * ldo + c, g * sigmoid_f(alpha * g) * (u + 1.f));
+}
+
+// the same, eight bfloat16 a thread (rows and columns on 16-byte boundaries)
+__global__ void gate_mul_clamped_bf16x8_kernel(const __nv_bfloat16* a, int lda, const __nv_bfloat16* b, int ldb, __nv_bfloat16* out,
+                                               int ldo, int rows, int cols8, float limit, float alpha) {
+    pdl_wait();                 // chained launch: nothing is read before the kernels ahead have finished
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols8) return;
+    const int r = (int)(i / cols8), c = (int)(i - (long long)r * cols8) * 8;
+    const uint4 ga = *reinterpret_cast<const uint4*>(a + (size_t)r * lda + c), va = *reinterpret_cast<const uint4*>(b + (size_t)r * ldb + c);
+    const uint32_t gw[4] = {ga.x, ga.y, ga.z, ga.w}, vw[4] = {va.x, va.y, va.z, va.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float g0 = fminf(__uint_as_float(gw[k] << 16), limit), g1 = fminf(__uint_as_float(gw[k] & 0xffff0000u), limit);
+        const float v0 = fminf(fmaxf(__uint_as_float(vw[k] << 16), -limit), limit), v1 = fminf(fmaxf(__uint_as_float(vw[k] & 0xffff0000u), -limit), limit);
+        const __nv_bfloat162 p = __floats2bfloat162_rn(g0 * sigmoid_f(alpha * g0) * (v0 + 1.f), g1 * sigmoid_f(alpha * g1) * (v1 + 1.f));
+        o[k] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 constexpr int NORM_THREADS = 128;
 constexpr int NORM_MAX_GROUPS = 1024;
@@ -407,6 +442,28 @@ extern "C" int vlrf_cast_rows(const float* x, void* out, int out_dtype, long lon
 static int gate_mul_any(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
                         int out_dtype, int rows, int cols, int per, int act, cudaStream_t stream);
 
+extern "C" int vlrf_gate_mul_clamped(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
+                                     int out_dtype, int rows, int cols, float limit, float alpha, cudaStream_t stream) {
+    VLRF_REQUIRE(rows >= 0 && cols > 0 && lda >= cols && ldb >= cols && ldo >= cols, "gate_mul_clamped: bad sizes");
+    VLRF_REQUIRE(limit > 0.f, "gate_mul_clamped: the bound %f is not positive", (double)limit);
+    if (rows == 0) return VLRF_OK;
+    const long long n = (long long)rows * cols;
+    const dim3 blocks((unsigned)((n + 255) / 256));
+    typedef __nv_bfloat16 bf;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                         cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0;
+#define GO(AT, BT, OT) launch_chained(gate_mul_clamped_kernel<AT, BT, OT>, blocks, dim3(256), (size_t)0, stream, (const AT*)a, lda, (const BT*)b, ldb, (OT*)out, ldo, rows, cols, limit, alpha)
+    if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16 && aligned)
+        launch_chained(gate_mul_clamped_bf16x8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), (size_t)0, stream, (const bf*)a, lda,
+                       (const bf*)b, ldb, (bf*)out, ldo, rows, cols / 8, limit, alpha);
+    else if (a_dtype == VLRF_BF16 && b_dtype == VLRF_BF16 && out_dtype == VLRF_BF16) GO(bf, bf, bf);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_F32) GO(float, float, float);
+    else if (a_dtype == VLRF_F32 && b_dtype == VLRF_F32 && out_dtype == VLRF_BF16) GO(float, float, bf);
+    else return vlrf_fail(VLRF_ERR_INVALID_ARG, "gate_mul_clamped: dtypes %d, %d -> %d are not taken", a_dtype, b_dtype, out_dtype);
+#undef GO
+    return vlrf_check_launch("gate_mul_clamped");
+}
+
 extern "C" int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
                              int out_dtype, int rows, int cols, int act, cudaStream_t stream) {
     return gate_mul_any(a, lda, a_dtype, b, ldb, b_dtype, out, ldo, out_dtype, rows, cols, 1, act, stream);
@@ -421,7 +478,8 @@ extern "C" int vlrf_gate_mul_groups(const void* a, int lda, int a_dtype, const v
 static int gate_mul_any(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo,
                         int out_dtype, int rows, int cols, int per, int act, cudaStream_t stream) {
     VLRF_REQUIRE(rows >= 0 && cols > 0 && per > 0 && lda >= cols / per && ldb >= cols && ldo >= cols, "gate_mul: bad sizes");
-    VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID || act == VLRF_ACT_RELU, "gate_mul: the gate is x*sigmoid(x), sigmoid(x) or max(x, 0), not %d", act);
+    VLRF_REQUIRE(act == VLRF_ACT_SILU || act == VLRF_ACT_SIGMOID || act == VLRF_ACT_RELU || act == VLRF_ACT_GELU_TANH,
+                 "gate_mul: the gate is x*sigmoid(x), sigmoid(x), max(x, 0) or the tanh form of GELU, not %d", act);
     if (rows == 0) return VLRF_OK;
     const long long n = (long long)rows * cols;
     const dim3 blocks((unsigned)((n + 255) / 256));

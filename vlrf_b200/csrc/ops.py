@@ -15,7 +15,7 @@ from . import KernelError, call
 F32, BF16 = 0, 1
 ACT = {"none": 0, None: 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3}
 #: gates of `gate_mul` (not taken by the products' epilogues)
-GATE = {"silu": 4, "sigmoid": 5, "relu": 6}
+GATE = {"silu": 4, "sigmoid": 5, "relu": 6, "gelu_tanh": 1}
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -844,10 +844,12 @@ def moe_route(z, n_experts: int, top: int, shared_gate: bool, tok_slot, ids, wts
 
 
 def moe_route_scored(z, n_outputs: int, top: int, groups: int, keep: int, n_identity: int, scale: float, correction, tok_slot,
-                     ids, wts, rank, counts, n_tokens: int) -> None:
-    """From float32 router logits z [T, ≥ n_outputs]: softmax over all outputs, the choice by score + correction inside the
-    `keep` best of `groups` groups, weights score · scale; the last n_identity outputs get id −2 and no rank (see the
-    kernel library's header)."""
+                     ids, wts, rank, counts, n_tokens: int, scoring: str = "softmax") -> None:
+    """From float32 router logits z [T, ≥ n_outputs]: softmax over all outputs (scoring "sigmoid": the sigmoid of each),
+    the choice by score + correction inside the `keep` best of `groups` groups, weights score · scale; the last
+    n_identity outputs get id −2 and no rank (see the kernel library's header)."""
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route_scored: scoring '{scoring}' is neither 'softmax' nor 'sigmoid'")
     _rows(z, "z", torch.float32); _dev(ids, "ids", torch.int32); _dev(wts, "wts", torch.float32)
     _dev(rank, "rank", torch.int32); _dev(counts, "counts", torch.int32); _dev(correction, "correction", torch.float32)
     if tok_slot is not None:
@@ -856,7 +858,7 @@ def moe_route_scored(z, n_outputs: int, top: int, groups: int, keep: int, n_iden
             or counts.numel() < max(n_outputs - n_identity, 1):
         raise KernelError("moe_route_scored: sizes do not match")
     call("vlrf_moe_route_scored", _ptr(z), z.stride(0), n_outputs, top, int(groups), int(keep), int(n_identity), float(scale),
-         _ptr(correction), _ptr(tok_slot), _ptr(ids), _ptr(wts), _ptr(rank), _ptr(counts), n_tokens, _stream())
+         1 if scoring == "sigmoid" else 0, _ptr(correction), _ptr(tok_slot), _ptr(ids), _ptr(wts), _ptr(rank), _ptr(counts), n_tokens, _stream())
 
 
 def moe_plan(counts, offsets, n_experts: int) -> None:
@@ -956,12 +958,48 @@ def softcap(values, n_rows: int, cap: float) -> None:
     call("vlrf_softcap", _ptr(values), n_rows * values.shape[1], float(cap), _stream())
 
 
+def embed_bigram(table, pairs, buckets: int, mul_prev: int, mul_cur: int, scale: float, kept, ctx, out) -> None:
+    """out[t] = table[token] · scale + pairs[(token before · mul_prev + token · mul_cur) mod buckets] (pairs[buckets] for a
+    sequence's first token): float32 [T, d].  kept: int32 [slots, 2], every sequence's last token by the parity of its
+    length (see the kernel library's header)."""
+    _dev(table, "table"); _dev(pairs, "pairs", table.dtype); _dev(kept, "kept", torch.int32); _dev(out, "out", torch.float32)
+    V, d = table.shape
+    if tuple(pairs.shape) != (buckets + 1, d) or out.shape[0] < ctx.n_tokens or out.shape[1] != d or kept.dim() != 2 \
+            or kept.shape[1] != 2 or not kept.is_contiguous():
+        raise KernelError("embed_bigram: sizes do not match")
+    call("vlrf_embed_bigram", _ptr(table), _ptr(pairs), dtype_code(table.dtype), _ptr(ctx.tokens), _ptr(ctx.tok_slot), _ptr(ctx.tok_pos),
+         _ptr(ctx.seq_start), ctx.n_seqs, _ptr(kept), _ptr(out), ctx.n_tokens, d, V, int(buckets), int(mul_prev), int(mul_cur),
+         float(scale), _ptr(ctx.dev_err), _stream())
+
+
+def scale_values(values, n_rows: int, factor: float) -> None:
+    """values[:n_rows] ← values · factor, float32, in place."""
+    _dev(values, "values", torch.float32)
+    call("vlrf_scale_values", _ptr(values), n_rows * values.shape[1], float(factor), _stream())
+
+
+def gate_mul_clamped(a, b, out, limit: float, alpha: float, n_rows: int, cols: int) -> None:
+    """out[r, :cols] = g · sigmoid(alpha · g) · (u + 1) with g = min(a, limit), u = clamp(b, −limit, limit); a, b and out may be
+    column ranges of wider rows, and out may be a or b."""
+    for name, t in (("a", a), ("b", b), ("out", out)):
+        _rows(t, name)
+        if t.shape[0] < n_rows or t.shape[1] < cols:
+            raise KernelError(f"gate_mul_clamped: {name} does not match")
+    call("vlrf_gate_mul_clamped", _ptr(a), a.stride(0), dtype_code(a.dtype), _ptr(b), b.stride(0), dtype_code(b.dtype), _ptr(out),
+         out.stride(0), dtype_code(out.dtype), n_rows, cols, float(limit), float(alpha), _stream())
+
+
 # ---- attention with key and value sizes of their own ---------------------------------------------------------------------
 
 def qkv_rope_append(proj, q_off: int, k_off: int, v_off: int, freq, rot: int, q_out, k_cache, v_cache, block_table, tok_slot,
-                    tok_pos, n_tokens: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, write_cache: bool, dev_err) -> None:
+                    tok_pos, n_tokens: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, write_cache: bool, dev_err, *,
+                    norm: str | None = None, q_norm=None, k_norm=None, eps: float = 0.0, interleaved: bool = False,
+                    magnitude: float = 1.0) -> None:
     """Queries (rotated) into q_out, keys (rotated) and values into the paged cache, from the float32 rows of a layer's
-    input product.  proj may be a range of columns of wider rows."""
+    input product.  proj may be a range of columns of wider rows.  norm "head" / "all": an RMS norm of queries and keys
+    ahead of the rotation, every head by itself (weights of dk entries shared by the heads) or the whole projection as
+    one row (weights of heads · dk entries); interleaved: entry 2i pairs with 2i + 1; magnitude: a factor on cosines and
+    sines.  With write_cache False the key and value columns are not read (k_off, v_off, k_norm are ignored)."""
     _rows(proj, "proj", torch.float32); _dev(q_out, "q_out"); _dev(k_cache, "k_cache", q_out.dtype); _dev(v_cache, "v_cache", q_out.dtype)
     _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32)
     nb, hkv, bt, kd = k_cache.shape
@@ -973,14 +1011,34 @@ def qkv_rope_append(proj, q_off: int, k_off: int, v_off: int, freq, rot: int, q_
             raise KernelError("qkv_rope_append: one frequency per rotated pair")
     if proj.shape[0] < n_tokens or q_out.shape[0] < n_tokens:
         raise KernelError("qkv_rope_append: fewer rows than tokens")
-    call("vlrf_qkv_rope_append", _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(freq) if rot > 0 else 0, int(rot), _ptr(q_out),
-         q_out.shape[1], _ptr(k_cache), _ptr(v_cache), dtype_code(q_out.dtype), _ptr(block_table), block_table.shape[1],
-         _ptr(tok_slot), _ptr(tok_pos), n_tokens, n_heads, n_kv_heads, dk, dv, bt, 1 if write_cache else 0, _ptr(dev_err), _stream())
+    code = {None: 0, "head": 1, "all": 2}.get(norm, -1)
+    if code < 0:
+        raise KernelError(f"qkv_rope_append: norm '{norm}' is neither 'head' nor 'all'")
+    if code:
+        _dev(q_norm, "q_norm", torch.float32)
+        if q_norm.numel() != (dk if code == 1 else n_heads * dk):
+            raise KernelError("qkv_rope_append: the queries' norm weights do not match")
+        if write_cache:
+            _dev(k_norm, "k_norm", torch.float32)
+            if k_norm.numel() != (dk if code == 1 else n_kv_heads * dk):
+                raise KernelError("qkv_rope_append: the keys' norm weights do not match")
+    call("vlrf_qkv_norm_rope_append", _ptr(proj), proj.stride(0), q_off, k_off if write_cache else 0, v_off if write_cache else 0,
+         _ptr(freq) if rot > 0 else 0, int(rot), _ptr(q_out), q_out.shape[1], _ptr(k_cache), _ptr(v_cache), dtype_code(q_out.dtype),
+         _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), n_tokens, n_heads, n_kv_heads, dk, dv, bt,
+         1 if write_cache else 0, code, _ptr(q_norm) if code else 0, _ptr(k_norm) if code and write_cache else 0, float(eps),
+         1 if interleaved else 0, float(magnitude), _ptr(dev_err), _stream())
 
 
 def attention_window(q, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, n_kv_heads: int,
-                     dk: int, dv: int, scale: float, window: int, out_scale: float, dev_err) -> None:
-    """Each token's queries attend the visible keys of its slot; out may be a range of columns of wider rows."""
+                     dk: int, dv: int, scale: float, window: int, out_scale: float, dev_err, *, softcap: float = 0.0,
+                     keep_first: int = 0, sink=None) -> None:
+    """Each token's queries attend the visible keys of its slot; out may be a range of columns of wider rows.  softcap > 0
+    squashes the scaled scores; keys at positions below keep_first stay visible whatever the window; sink: float32
+    [heads], exp(sink) joins the softmax's denominator."""
+    if sink is not None:
+        _dev(sink, "sink", torch.float32)
+        if sink.numel() != n_heads:
+            raise KernelError("attention_window: one sink per query head")
     _dev(q, "q"); _dev(k_cache, "k_cache", q.dtype); _dev(v_cache, "v_cache", q.dtype); _rows(out, "out", q.dtype)
     _dev(block_table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32)
     nb, hkv, bt, kd = k_cache.shape
@@ -988,9 +1046,9 @@ def attention_window(q, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n
         raise KernelError("attention_window: cache shape does not match the heads")
     if out.shape[1] < n_heads * dv or out.shape[0] < n_tokens or q.shape[0] < n_tokens:
         raise KernelError("attention_window: output does not match")
-    call("vlrf_attn_window", _ptr(q), dtype_code(q.dtype), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+    call("vlrf_attn_window_ex", _ptr(q), dtype_code(q.dtype), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
          block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.stride(0), n_tokens, n_heads, n_kv_heads, dk, dv, bt,
-         float(scale), int(window), float(out_scale), _ptr(dev_err), _stream())
+         float(scale), int(window), float(out_scale), float(softcap), int(keep_first), _ptr(sink), _ptr(dev_err), _stream())
 
 
 # ---- a state-space recurrence with a matrix state per head -----------------------------------------------------------------
@@ -1055,20 +1113,20 @@ def attention_window_kind(dtype: torch.dtype, dk: int, dv: int, n_heads: int, n_
     return {"prompt": kind, "decode": kind}
 
 
-def window_decode_splits(n_rows: int, n_kv_heads: int, max_context: int, window: int) -> int:
+def window_decode_splits(n_rows: int, n_kv_heads: int, max_context: int, window: int, keep_first: int = 0) -> int:
     """Into how many parts a decode step cuts each context for the tensor-core kernel: parts of at least two key tiles,
     about two CTAs an SM in all."""
     forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
     if forced:
         return max(1, min(16, int(forced)))
-    reach = min(max_context, window + 63) if window > 0 else max_context
+    reach = min(max_context, window + 63 + (-(-keep_first // 64)) * 64) if window > 0 else max_context
     tiles = -(-reach // 64)
     # (a part costs a second kernel that merges them: parts only where the step's CTAs would not fill the GPU otherwise)
     return max(1, min(16, tiles // 2, (2 * sm_count()) // max(1, n_rows * n_kv_heads)))
 
 
 def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, scale: float,
-                          window: int, out_scale: float) -> None:
+                          window: int, out_scale: float, *, softcap: float = 0.0, keep_first: int = 0, sink=None) -> None:
     """The attention of a step (prompt tokens, single tokens or a mix) with the kernel that suits it: bfloat16 sizes that
     the tensor-core kernel takes go there (a decode step's contexts cut into parts), everything else to the kernel
     that takes a warp per token and head."""
@@ -1078,16 +1136,20 @@ def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: i
         _rows(out, "out", q.dtype)
         n_split, partials = 1, None
         if ctx.max_new == 1:
-            n_split = window_decode_splits(ctx.n_tokens, n_kv_heads, ctx.max_context, window)
+            n_split = window_decode_splits(ctx.n_tokens, n_kv_heads, ctx.max_context, window, keep_first)
             if n_split > 1:
                 partials = ctx.ws.get("window_partials", ctx.n_tokens * n_heads * n_split, dv + 2, torch.float32)
-        call("vlrf_attn_window_mma", _ptr(q), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        if sink is not None:
+            _dev(sink, "sink", torch.float32)
+            if sink.numel() != n_heads:
+                raise KernelError("attention_window: one sink per query head")
+        call("vlrf_attn_window_mma_ex", _ptr(q), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(out), out.stride(0), _ptr(partials), ctx.n_seqs,
-             ctx.max_new, n_heads, n_kv_heads, dk, dv, bt, float(scale), int(window), float(out_scale), n_split, _ptr(ctx.dev_err),
-             _stream())
+             ctx.max_new, n_heads, n_kv_heads, dk, dv, bt, float(scale), int(window), float(out_scale), n_split, float(softcap),
+             int(keep_first), _ptr(sink), _ptr(ctx.dev_err), _stream())
         return
     attention_window(q, k_cache, v_cache, block_table, ctx.tok_slot, ctx.tok_pos, out, ctx.n_tokens, n_heads, n_kv_heads, dk, dv,
-                     scale, window, out_scale, ctx.dev_err)
+                     scale, window, out_scale, ctx.dev_err, softcap=softcap, keep_first=keep_first, sink=sink)
 
 
 def ssd_scan_step(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, ctx, y, n_heads: int, n_groups: int, n_state: int, p: int) -> None:

@@ -11,7 +11,13 @@
 // A write that is followed by the next sublayer's read is one kernel (write_read): one pass over the streams.
 //
 // embed_streams: x[t][s] = table[token[t]] · scale for every stream s (scale 1 and one stream: a plain lookup).
-// softcap: v ← cap · tanh(v / cap) over float32 rows (logits).
+// embed_bigram: x[t] = table[token[t]] · scale + pairs[row], one stream; row = (token before · mul_prev + token · mul_cur)
+//   mod buckets, and row `buckets` (the table's last) for a sequence's first token.  The token before is the row above
+//   where the step brings it, else the sequence's kept token: an int32 state [slot][2] holds each sequence's last token
+//   twice, a step reading the copy of the parity of the position it begins at and writing the copy of the parity of the
+//   position it ends at, so a step of one token leaves what it read and may run twice.  The CTA of a sequence's first
+//   token of the step also keeps the sequence's last token of the step, after its own read of the kept one.
+// softcap: v ← cap · tanh(v / cap) over float32 rows (logits).  scale_values: v ← v · factor.
 #include "common.cuh"
 
 namespace {
@@ -36,6 +42,58 @@ embed_streams_kernel(const WT* __restrict__ table, const int* __restrict__ token
         const float v = ElemIO<WT>::load(row + i) * scale;
         for (int s = 0; s < S; ++s) out[(size_t)s * d + i] = v;
     }
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(ST_THREADS)
+embed_bigram_kernel(const WT* __restrict__ table, const WT* __restrict__ pairs, const int* __restrict__ tokens,
+                    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ seq_start, int n_seqs,
+                    int* __restrict__ kept, float* __restrict__ x, int T, int d, int V, int buckets, int mul_prev, int mul_cur,
+                    float scale, int* __restrict__ dev_err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int row_sm;
+    const int t = blockIdx.x;
+    const int slot = tok_slot[t];
+    if (slot < 0) return;                     // padding row (the whole CTA leaves)
+    int id = tokens[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_TOKEN_RANGE);
+        id = min(max(id, 0), V - 1);
+    }
+    if (threadIdx.x == 0) {
+        const int pos = tok_pos[t];
+        const bool above = t > 0 && tok_slot[t - 1] == slot && tok_pos[t - 1] == pos - 1;   // the step brings the token before
+        int prev = -1;
+        if (above) prev = tokens[t - 1];
+        else {
+            if (pos > 0) prev = kept[(size_t)slot * 2 + (pos & 1)];
+            // this row begins its sequence's tokens of the step: find where they end and keep the last one
+            int lo = 0, hi = n_seqs - 1;
+            while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seq_start[mid] <= t) lo = mid; else hi = mid - 1; }
+            const int last = seq_start[lo + 1] - 1;
+            if (last >= t && last < T) kept[(size_t)slot * 2 + ((pos + (last - t) + 1) & 1)] = tokens[last];
+        }
+        int row = buckets;
+        if (pos > 0) {
+            prev = min(max(prev, 0), V - 1);
+            row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % buckets);
+            if (row < 0) row += buckets;
+        }
+        row_sm = row;
+    }
+    __syncthreads();
+    const WT* er = table + (size_t)id * d;
+    const WT* br = pairs + (size_t)row_sm * d;
+    float* out = x + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += ST_THREADS) out[i] = fmaf(ElemIO<WT>::load(er + i), scale, ElemIO<WT>::load(br + i));
+}
+
+__global__ void scale_values_kernel(float* __restrict__ v, long long n, float factor) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) v[i] *= factor;
 }
 
 template <typename OT>
@@ -222,6 +280,31 @@ extern "C" int vlrf_streams_write_read(float* x, const float* mix, const float* 
 #undef GO_S
 #undef GO
     return vlrf_check_launch("streams_write_read");
+}
+
+extern "C" int vlrf_embed_bigram(const void* table, const void* pairs, int w_dtype, const int* tokens, const int* tok_slot,
+                                 const int* tok_pos, const int* seq_start, int n_seqs, int* kept, float* x, int T, int d, int V,
+                                 int buckets, int mul_prev, int mul_cur, float scale, int* dev_err, cudaStream_t stream) {
+    VLRF_REQUIRE(T >= 0 && d > 0 && V > 0 && buckets > 0 && n_seqs >= 0, "embed_bigram: bad sizes");
+    VLRF_REQUIRE(dev_err != nullptr && kept != nullptr && seq_start != nullptr, "embed_bigram: needs the error word, the kept tokens and the sequences' rows");
+    if (T == 0 || n_seqs == 0) return VLRF_OK;
+    if (w_dtype == VLRF_F32)
+        launch_chained(embed_bigram_kernel<float>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, (const float*)table, (const float*)pairs,
+                       tokens, tok_slot, tok_pos, seq_start, n_seqs, kept, x, T, d, V, buckets, mul_prev, mul_cur, scale, dev_err);
+    else if (w_dtype == VLRF_BF16)
+        launch_chained(embed_bigram_kernel<__nv_bfloat16>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, (const __nv_bfloat16*)table,
+                       (const __nv_bfloat16*)pairs, tokens, tok_slot, tok_pos, seq_start, n_seqs, kept, x, T, d, V, buckets, mul_prev,
+                       mul_cur, scale, dev_err);
+    else
+        return vlrf_fail(VLRF_ERR_INVALID_ARG, "embed_bigram: unknown dtype %d", w_dtype);
+    return vlrf_check_launch("embed_bigram");
+}
+
+extern "C" int vlrf_scale_values(float* v, long long n, float factor, cudaStream_t stream) {
+    VLRF_REQUIRE(n >= 0, "scale_values: bad size");
+    if (n == 0) return VLRF_OK;
+    launch_chained(scale_values_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, stream, v, n, factor);
+    return vlrf_check_launch("scale_values");
 }
 
 extern "C" int vlrf_softcap(float* v, long long n, float cap, cudaStream_t stream) {

@@ -187,7 +187,7 @@ int vlrf_group_rmsnorm(const float* y, int ld_y, const int* rows, const float* w
                        int n_rows, int d, int groups, float eps, int accumulate, void* also_bf16, cudaStream_t stream);
 // n float32 numbers to out_dtype.
 int vlrf_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
-// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU, VLRF_ACT_SIGMOID or VLRF_ACT_RELU, each with a row stride of its own (out may be
+// out[r][c] = act(a[r][c]) · b[r][c], act VLRF_ACT_SILU, VLRF_ACT_SIGMOID, VLRF_ACT_RELU or VLRF_ACT_GELU_TANH, each with a row stride of its own (out may be
 // a or b).  Dtypes (a, b → out): all bfloat16; all float32; float32, bfloat16 → bfloat16; float32, float32 → bfloat16.
 int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
                   int rows, int cols, int act, cudaStream_t stream);
@@ -195,6 +195,10 @@ int vlrf_gate_mul(const void* a, int lda, int a_dtype, const void* b, int ldb, i
 // per head on the merged heads); cols a multiple of per.
 int vlrf_gate_mul_groups(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
                          int rows, int cols, int per, int act, cudaStream_t stream);
+// A gate with bounds: out[r][c] = g · sigmoid(alpha · g) · (u + 1) with g = min(a[r][c], limit) and u = clamp(b[r][c], −limit,
+// limit).  Dtypes (a, b → out): all bfloat16; all float32; float32, float32 → bfloat16.
+int vlrf_gate_mul_clamped(const void* a, int lda, int a_dtype, const void* b, int ldb, int b_dtype, void* out, int ldo, int out_dtype,
+                          int rows, int cols, float limit, float alpha, cudaStream_t stream);
 // Plain RMS norm and token shift of the step's residual rows: with n_t = x[t] / sqrt(mean(x[t]²) + eps) · w,
 // out[t] = n_t + (n_before − n_t) · mu, n_before being the normed row of the sequence's token before: the row above
 // where tok_slot[t−1] = tok_slot[t], zeros at position 0, else the sequence's kept row.  state: float32 [slots][2][d];
@@ -223,6 +227,15 @@ int vlrf_streams_write_read(float* x, const float* mix, const float* b, const fl
                             int out_dtype, int T, int d, int S, float eps, cudaStream_t stream);
 // v ← cap · tanh(v / cap) over n float32 numbers.
 int vlrf_softcap(float* v, long long n, float cap, cudaStream_t stream);
+// v ← v · factor over n float32 numbers.
+int vlrf_scale_values(float* v, long long n, float factor, cudaStream_t stream);
+// x[t] = table[tokens[t]] · scale + pairs[row]: float32 [T][d] from tables [V][d] and [buckets + 1][d] of w_dtype; row =
+// (token before · mul_prev + token · mul_cur) mod buckets, or `buckets` at position 0.  The token before is the row above
+// where tok_slot and tok_pos say so, else kept[slot][position & 1]; kept int32 [slots][2] receives every sequence's last
+// token of the step at the parity of the position behind it (seq_start: n_seqs + 1 first rows of the sequences' tokens).
+int vlrf_embed_bigram(const void* table, const void* pairs, int w_dtype, const int* tokens, const int* tok_slot, const int* tok_pos,
+                      const int* seq_start, int n_seqs, int* kept, float* x, int T, int d, int V, int buckets, int mul_prev,
+                      int mul_cur, float scale, int* dev_err, cudaStream_t stream);
 
 // ---- attention with key and value sizes of their own (attention_window.cu) -------------------------------------------------
 // From the float32 rows of a layer's input product (queries at q_off: H·dk columns, keys at k_off: Hkv·dk, values at
@@ -233,11 +246,28 @@ int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_off, int v_
                          int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks, const int* tok_slot,
                          const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT, int write_cache, int* dev_err,
                          cudaStream_t stream);
+// The same with an RMS norm of queries and keys ahead of the rotation (norm 1: every head by itself with one weight vector
+// of dk entries for all heads; norm 2: all heads of the projection as one row, weights of H·dk and Hkv·dk entries; 0: none),
+// the pairing of rotated entries (0: entry i with i + rot/2; 1: entry 2i with 2i + 1) and a factor on every cosine and
+// sine.  Values are read as projected, so v_off = k_off keeps the keys from before norm and rotation as values.  With
+// write_cache = 0 the key and value columns are not read.
+int vlrf_qkv_norm_rope_append(const float* proj, int ld, int q_off, int k_off, int v_off, const float* freq, int rot, void* q_out,
+                              int ldq, void* Kc, void* Vc, int dtype, const int* block_table, int max_blocks, const int* tok_slot,
+                              const int* tok_pos, int T, int H, int Hkv, int dk, int dv, int BT, int write_cache, int norm,
+                              const float* q_norm, const float* k_norm, float eps, int pairing, float magnitude, int* dev_err,
+                              cudaStream_t stream);
 // out[t][h·dv …] = out_scale · softmax over the visible keys of (q·k · scale) · V: a token sees the keys of its slot at
 // positions ≤ its own (window > 0: the last `window` of them, itself included).  Any dk, dv up to 256.
 int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                      const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
                      float scale, int window, float out_scale, int* dev_err, cudaStream_t stream);
+// The same with a cap on the scores (softcap > 0: score ← softcap · tanh(score / softcap), after the scale), keys at
+// positions below keep_first visible whatever the window, and sink (null, or a float32 per query head): exp(sink[h])
+// is added to the softmax's denominator, with no key and no value.
+int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                        const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
+                        float scale, int window, float out_scale, float softcap, int keep_first, const float* sink, int* dev_err,
+                        cudaStream_t stream);
 
 // The same attention on the tensor cores (attention_window_mma.cu; bfloat16): a CTA per key/value head, sequence and tile
 // of 64 (token, query head) rows, for prompt steps (rows seq_start[i] … of q are sequence i's new tokens, the first at
@@ -248,6 +278,11 @@ int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, const void* Vc,
                          const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                          int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale,
                          int n_split, int* dev_err, cudaStream_t stream);
+// … with the cap, the kept first keys and the sinks of vlrf_attn_window_ex.
+int vlrf_attn_window_mma_ex(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
+                            const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
+                            int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale,
+                            int n_split, float softcap, int keep_first, const float* sink, int* dev_err, cudaStream_t stream);
 
 // ---- a state-space recurrence with a matrix state per head (ssd.cu) ----------------------------------------------------------
 // What a sequence keeps lies in `state`, float32 [slots][2][state_row]: per copy the heads' states [H][N][P] and, at
@@ -335,9 +370,9 @@ int vlrf_moe_route(const float* z, int ld_z, int E, int top, int shared_gate, co
 // the outputs of the `keep` best of `groups` equal groups of neighbours (a group's score: its largest s + correction;
 // ties to the lower index everywhere) and weighs the chosen by s · scale.  The last n_identity outputs stand for
 // experts without matrices that return their input: such a pair gets ids −2 and no row (padding rows: −1); counts
-// int32 [E − n_identity], zero before.  top ≤ keep · E / groups.
+// int32 [E − n_identity], zero before.  top ≤ keep · E / groups.  scoring 1: s = sigmoid(z), each output by itself.
 int vlrf_moe_route_scored(const float* z, int ld_z, int E, int top, int groups, int keep, int n_identity, float scale,
-                          const float* correction, const int* tok_slot, int* ids, float* wts, int* rank, int* counts, int T,
+                          int scoring, const float* correction, const int* tok_slot, int* ids, float* wts, int* rank, int* counts, int T,
                           cudaStream_t stream);
 // offsets[e] = Σ counts[< e], E + 1 entries; counts are left zero.
 int vlrf_moe_plan(int* counts, int* offsets, int E, cudaStream_t stream);

@@ -84,9 +84,12 @@ class DecoderModel:
         return out
 
     def cache_needs(self) -> list:
-        """For every schedule entry what it keeps per sequence (None for entries that read another's)."""
-        return [None if c.reads_cache_of is not None else self.layers[c.layer].cache_need()
-                for c in self.schedule]
+        """For every schedule entry what it keeps per sequence (None for entries that read another's); behind them, where
+        the embedding keeps something per sequence (say, the token before), one more entry with its need."""
+        needs = [None if c.reads_cache_of is not None else self.layers[c.layer].cache_need()
+                 for c in self.schedule]
+        own = self.embedding.cache_need() if hasattr(self.embedding, "cache_need") else None
+        return needs + [own] if own is not None else needs
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -138,7 +141,10 @@ class DecoderModel:
         ctx.ws.row_stats.forget()                      # nothing is known about the rows of the step before
         ctx.ws.input_cast = None
         ctx.ws.normed_ready = None
-        self.embedding(ctx, x)
+        if len(cache.needs) > len(self.schedule):      # the embedding keeps something per sequence
+            self.embedding(ctx, x, state=cache.view(len(self.schedule)).state)
+        else:
+            self.embedding(ctx, x)
         if not getattr(self.embedding, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
         for i, call in enumerate(self.schedule):

@@ -56,12 +56,12 @@ class DenseMLP:
         ops.linear(u, self.w_out, self.b_out, x, residual=x if accumulate else None, stats=ctx.ws.row_stats)
 
 
-GATES = ("silu", "relu", "sigmoid")
+GATES = ("silu", "relu", "sigmoid", "gelu_tanh")
 
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP:
-    """x += (act(h·W_gateᵀ) · (h·W_upᵀ))·W_downᵀ; act "silu", "relu" or "sigmoid".  Gate and up are one product with
+    """x += (act(h·W_gateᵀ) · (h·W_upᵀ))·W_downᵀ; act "silu", "relu", "sigmoid" or "gelu_tanh" (the tanh form of GELU).  Gate and up are one product with
     float32 results, the gate is applied in float32 and the inner rows are rounded once; the residual sum runs in the
     second product's epilogue (`accumulate=False`: the result replaces x instead)."""
 

@@ -10,7 +10,9 @@ What else is a parameter.  An expert without a gate (`w_gate=None`): W_down relu
 weights do not see it) among the outputs of the `keep` best of `groups` equal groups of neighbours, a group's score
 being its largest s + correction, and weighs the chosen by s · `weight_scale` without renormalizing.  Identity
 experts (`n_identity`): the router's last n_identity outputs stand for experts without matrices that return their
-input, so the router has n_identity more rows than there are expert matrices.
+input, so the router has n_identity more rows than there are expert matrices.  `scoring="sigmoid"`: the same rule with
+s = sigmoid(z), each output by itself.  `gate="clamped"` (with `limit`, `gate_alpha`): an expert is
+W_down (g · sigmoid(gate_alpha · g) · (u + 1)) with g = min(W_gate h, limit) and u = clamp(W_up h, −limit, limit).
 
 Nothing is decided on the host: the router's kernel counts each expert's rows, the tokens' inputs are copied into a
 buffer sorted by expert, and two grouped products (each row block with its expert's matrix) run over it with the gate
@@ -30,7 +32,8 @@ from .registry import register_part
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts:
     def __init__(self, w_router, b_router, w_gate, w_up, w_down, *, top: int, shared=None, scoring: str = "softmax_chosen",
-                 correction=None, groups: int = 1, keep: int = 1, weight_scale: float = 1.0, n_identity: int = 0):
+                 correction=None, groups: int = 1, keep: int = 1, weight_scale: float = 1.0, n_identity: int = 0,
+                 gate: str = "silu", limit: float | None = None, gate_alpha: float = 1.0):
         """w_router [E + n_identity, width], b_router [E + n_identity] float32 or None; w_gate (or None), w_up [E, ff, width],
         w_down [E, width, ff]; shared: None or (w_gate [ffs, width], w_up [ffs, width], w_down [width, ffs], w_sg [1, width]
         or None); correction: float32 [E + n_identity] or None."""
@@ -44,8 +47,11 @@ class RoutedExperts:
                 raise ValueError("routed experts: the experts' gate and up matrices are [experts, ff, width]")
             if tuple(w_down.shape) != (E, width, ff):
                 raise ValueError("routed experts: the experts' down matrices are [experts, width, ff]")
-        if scoring not in ("softmax_chosen", "softmax_all"):
-            raise ValueError(f"routed experts: scoring '{scoring}' is neither 'softmax_chosen' nor 'softmax_all'")
+        if scoring not in ("softmax_chosen", "softmax_all", "sigmoid"):
+            raise ValueError(f"routed experts: scoring '{scoring}' is none of 'softmax_chosen', 'softmax_all', 'sigmoid'")
+        if gate not in ("silu", "clamped") or (gate == "clamped" and (w_gate is None or limit is None or not limit > 0.0)):
+            raise ValueError("routed experts: the experts' gate is 'silu', or 'clamped' with gate matrices and a positive limit")
+        self.gate, self.limit, self.gate_alpha = gate, float(limit) if limit is not None else 0.0, float(gate_alpha)
         if scoring == "softmax_chosen" and (n_identity or correction is not None or groups != 1 or weight_scale != 1.0):
             raise ValueError("routed experts: identity experts, a correction, groups and a weight scale belong to scoring 'softmax_all'")
         if groups < 1 or n_out % groups != 0 or not (1 <= keep <= groups):
@@ -54,12 +60,12 @@ class RoutedExperts:
             raise ValueError(f"routed experts: a token takes 1…min(32, {keep * (n_out // groups)}) experts, not {top}")
         if n_out > ops.MOE_MAX_OUTPUTS:
             raise ValueError(f"routed experts: the router's kernel takes up to {ops.MOE_MAX_OUTPUTS} outputs, not {n_out}")
-        if b_router is not None and scoring == "softmax_all":
-            raise ValueError("routed experts: scoring 'softmax_all' has a correction of the choice, not a bias of the logits")
+        if b_router is not None and scoring != "softmax_chosen":
+            raise ValueError(f"routed experts: scoring '{scoring}' has a correction of the choice, not a bias of the logits")
         self.n_experts, self.n_outputs, self.n_identity, self.top, self.width, self.ff = E, n_out, int(n_identity), int(top), width, ff
         self.scoring, self.groups, self.keep, self.weight_scale = scoring, int(groups), int(keep), float(weight_scale)
         self.correction = None
-        if scoring == "softmax_all":
+        if scoring != "softmax_chosen":
             self.correction = (correction.float() if correction is not None
                                else torch.zeros(n_out, dtype=torch.float32, device=w_router.device)).contiguous()
             if tuple(self.correction.shape) != (n_out,):
@@ -116,9 +122,9 @@ class RoutedExperts:
         gate = ws.get("moe_shared_gate", T, 1, torch.float32) if self.shared_gate else None
         counts = ws.get_zeroed("moe_counts", max(E, 1), torch.int32)
         offsets = ws.get("moe_offsets", 1, max(E, 1) + 1, torch.int32)
-        if self.scoring == "softmax_all":
+        if self.scoring != "softmax_chosen":
             ops.moe_route_scored(z, self.n_outputs, top, self.groups, self.keep, self.n_identity, self.weight_scale, self.correction,
-                                 ctx.tok_slot, ids, wts, rank, counts, T)
+                                 ctx.tok_slot, ids, wts, rank, counts, T, scoring="sigmoid" if self.scoring == "sigmoid" else "softmax")
         else:
             ops.moe_route(z, E, top, self.shared_gate, ctx.tok_slot, ids, wts, rank, gate, counts, T)
         ops.moe_plan(counts, offsets, max(E, 1))
@@ -130,7 +136,10 @@ class RoutedExperts:
             if self.gated:
                 u = ws.get("moe_gate_up", P, 2 * ff, act)
                 ops.linear_grouped(rows, self.w_gate_up, u, offsets, P)
-                ops.gate_mul(u[:, :ff], u[:, ff:], a, "silu", P, ff)
+                if self.gate == "clamped":
+                    ops.gate_mul_clamped(u[:, :ff], u[:, ff:], a, self.limit, self.gate_alpha, P, ff)
+                else:
+                    ops.gate_mul(u[:, :ff], u[:, ff:], a, "silu", P, ff)
             else:
                 ops.linear_grouped(rows, self.w_gate_up, a, offsets, P, act="relu2")     # (the activation in the product's epilogue)
             ops.linear_grouped(a, self.w_down, out, offsets, P)

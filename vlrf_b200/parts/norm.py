@@ -34,11 +34,23 @@ class GroupRMSNorm:
     """The row is cut into `groups` equal consecutive parts; each part is divided by sqrt(mean(part²) + eps) of its
     own, and the whole row is multiplied by weight.  One group is the plain RMS norm.  Sums and the division are
     float32.  `accumulate=True` adds the result to the (float32) output rows instead of replacing them, which is
-    what a block needs that norms a sublayer's output before the residual sum."""
+    what a block needs that norms a sublayer's output before the residual sum.
 
-    def __init__(self, weight: torch.Tensor, eps: float, groups: int = 1):
+    `offset` is added to the stored weight (1.0 for weights that are stored around zero, y = x̂ · (1 + w)), and
+    `post_scale`, a vector, multiplies the normed row element by element (a layer scale on a sublayer's normed output);
+    both are folded into one float32 factor per column when the part is made."""
+
+    def __init__(self, weight: torch.Tensor, eps: float, groups: int = 1, offset: float = 0.0, post_scale: torch.Tensor | None = None):
         if weight.dim() != 1 or groups < 1 or weight.shape[0] % groups != 0:
             raise ValueError(f"GroupRMSNorm: {tuple(weight.shape)} weights cannot be cut into {groups} equal parts")
+        if post_scale is not None and post_scale.shape != weight.shape:
+            raise ValueError("GroupRMSNorm: the scale behind the norm has one number per column")
+        self.stored_weight, self.offset, self.post_scale = weight, float(offset), post_scale
+        if offset != 0.0 or post_scale is not None:
+            weight = weight.float() + float(offset)
+            if post_scale is not None:
+                weight = weight * post_scale.float()
+            weight = weight.contiguous()
         self.weight, self.eps, self.groups = weight, float(eps), int(groups)
         self.width = weight.shape[0]
 
