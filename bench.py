@@ -854,6 +854,182 @@ def rakelorn_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
     return out
 
 
+#: Suposun at two sizes that resemble a real model's layers, beside a Kuvusun of the same width, depth, heads, head sizes and
+#: feed-forwards (its closest relative in the framework: the same block with the norm on the sublayers' outputs, the
+#: embedding as head, dense and routed feed-forwards, a layer that reads another's cache).  Layers: attention over all
+#: keys + dense; windowed attention with kept first keys, cap, sinks and gate + experts; attention reading the first
+#: layer's keys + experts; windowed attention + experts.
+SUPOSUN_SIZES = {
+    "s": dict(DESIGN_SIZES["s"], kv_heads=4, window=512, keep=64, ff_gated=2816, buckets=65521),
+    "m": dict(DESIGN_SIZES["m"], kv_heads=2, window=1024, keep=128, ff_gated=5632, buckets=65521),
+}
+
+
+def suposun_config(z: dict) -> dict:
+    def att(kind, **more):
+        m = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "rot": {"base": 1e6, "dims": z["rot"]}}
+        m.update(more)
+        return {"type": kind, "mixer": m}
+    win = att("attention", softcap=30.0, mask={"size": z["window"], "keep_first": z["keep"]})
+    win["mixer"]["rot"] = {"base": 1e6, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layers = [dict(att("attention_2"), mlp={"kind": "dense", "ff": z["ff_gated"]}), dict(win, mlp=moe),
+              dict(att("attention_2", kv_from=0), mlp=moe), dict(win, mlp=moe)]
+    return {"architecture": "Suposun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": z["buckets"], "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
+def suposun_kernels(z: dict, hbm_gbs: float, bf16_tflops: float) -> dict:
+    """Suposun's own kernels alone, each beside the like kernel of a model that was there (20 launches replayed as one graph,
+    inputs rotated over more than L2): attention with cap, kept first keys and sinks beside the same kernel with a plain
+    window (Kotisun's), in a prompt step and in a decode step; the preparation of queries and keys with their norm beside
+    the one without; the router by sigmoid scores beside Rakelorn's by a softmax; the experts' bounded gate beside
+    Kuvusun's; the dense feed-forward's GELU gate beside Kotisun's relu gate; the embedding with its bigram row beside
+    Kotisun's scaled embedding."""
+    import types
+    import torch
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.parts.context import Workspace
+    dev, bf = "cuda", torch.bfloat16
+    width, H, G, dk = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    window, keep = z["window"], z["keep"]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)   # noqa: E731
+
+    def timed(fn, reps=20):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    def bytes_point(us, nbytes):
+        return {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / hbm_gbs, 3), "mib": round(nbytes / 2**20, 1)}
+
+    def flops_point(us, fl):
+        return {"us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "frac_tensor": round(fl / us / 1e6 / bf16_tflops, 4)}
+
+    warm = torch.zeros(4096, 4096, device=dev)
+    t_end = time.time() + 0.2
+    while time.time() < t_end:
+        warm.add_(1.0)
+        torch.cuda.synchronize()
+    del warm
+    out = {}
+    S, L, B = 2, 1024, 64
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    sink = torch.randn(H, device=dev)
+    # -- attention over a paged cache whose blocks are dealt at random; several caches, so that a launch finds none in L2 -----
+    for label, n_seq, n_new, ctx_len in (("prompt", S, L, L), ("decode", B, 1, L)):
+        blocks_per = (ctx_len + 63) // 64
+        nb = n_seq * blocks_per
+        per_cache = nb * G * 64 * dk * 2 * 2
+        n_c = max(2, int(300e6 // per_cache) + 1) if label == "decode" else 2
+        caches = [(torch.randn(nb, G, 64, dk, device=dev).to(bf), torch.randn(nb, G, 64, dk, device=dev).to(bf)) for _ in range(n_c)]
+        table = torch.randperm(nb, device=dev).to(torch.int32).view(n_seq, blocks_per).contiguous()
+        T = n_seq * n_new
+        q = torch.randn(T, H * dk, device=dev).to(bf)
+        o = torch.zeros(T, H * dk, dtype=bf, device=dev)
+        c = types.SimpleNamespace(n_tokens=T, n_seqs=n_seq, max_new=n_new, max_context=ctx_len, ws=Workspace(dev), dev_err=err,
+                                  seq_slot=i32(list(range(n_seq))), seq_start=i32([i * n_new for i in range(n_seq + 1)]),
+                                  seq_pos0=i32([ctx_len - n_new] * n_seq), tok_slot=i32([s for s in range(n_seq) for _ in range(n_new)]),
+                                  tok_pos=i32([ctx_len - n_new + j for _ in range(n_seq) for j in range(n_new)]))
+        run = lambda i, **kw: ops.attention_window_step(q, caches[i % n_c][0], caches[i % n_c][1], table, o, c, H, G, dk, dk, dk ** -0.5, window, 1.0, **kw)  # noqa: E731
+        us_new = timed(lambda i: run(i, softcap=30.0, keep_first=keep, sink=sink))
+        us_old = timed(lambda i: run(i))
+        if label == "decode":
+            seen_new, seen_old = min(ctx_len, window + keep), min(ctx_len, window)
+            out["attention_decode"] = {"suposun": bytes_point(us_new, n_seq * G * seen_new * dk * 4),
+                                       "plain_window": bytes_point(us_old, n_seq * G * seen_old * dk * 4)}
+        else:
+            def pairs(extra):       # (query, key) pairs a head computes: the window's, and the kept keys where the window has left them
+                return sum(min(p + 1, window) + (min(extra, max(0, p + 1 - window)) if extra else 0) for p in range(n_new))
+            out["attention_prompt"] = {"suposun": flops_point(us_new, 4.0 * n_seq * H * dk * pairs(keep)),
+                                       "plain_window": flops_point(us_old, 4.0 * n_seq * H * dk * pairs(0))}
+        del caches
+    pctx = types.SimpleNamespace(n_tokens=S * L, n_seqs=S, seq_start=i32([0, L, 2 * L]), tok_slot=i32([s for s in range(S) for _ in range(L)]),
+                                 tok_pos=i32(list(range(L)) * S), dev_err=err)
+    dctx = types.SimpleNamespace(n_tokens=B, n_seqs=B, seq_start=i32(list(range(B + 1))), tok_slot=i32(list(range(B))), tok_pos=i32([L] * B), dev_err=err)
+    for label, c, rows in (("prompt", pctx, S * L), ("decode", dctx, B)):
+        # -- queries and keys: norm per head + rotation of neighbours + append, beside rotation + append ------------------------
+        in_w = H * dk + G * dk + H
+        n_p = max(2, int(300e6 // (rows * in_w * 4)) + 1)
+        projs = [torch.randn(rows, in_w, device=dev) for _ in range(n_p)]
+        nbk = max(S, B) * ((L + 64) // 64 + 1)
+        kc, vc = torch.zeros(nbk, G, 64, dk, dtype=bf, device=dev), torch.zeros(nbk, G, 64, dk, dtype=bf, device=dev)
+        table = torch.arange(nbk, dtype=torch.int32, device=dev).view(max(S, B), -1).contiguous()
+        qo = torch.zeros(rows, H * dk, dtype=bf, device=dev)
+        freq = torch.tensor([1e6 ** (-2.0 * i / z["rot"]) for i in range(z["rot"] // 2)], device=dev)
+        wn = torch.ones(dk, device=dev)
+        moved = rows * (in_w - H) * 4 + rows * (H + 2 * G) * dk * 2
+        us = timed(lambda i: ops.qkv_rope_append(projs[i % n_p], 0, H * dk, H * dk, freq, z["rot"], qo, kc, vc, table, c.tok_slot, c.tok_pos, rows, H, G,
+                                                 dk, dk, True, err, norm="head", q_norm=wn, k_norm=wn, eps=1e-6, interleaved=True, magnitude=1.2))
+        out["prepare_" + label] = {"suposun": bytes_point(us, moved)}
+        us = timed(lambda i: ops.qkv_rope_append(projs[i % n_p], 0, H * dk, H * dk, freq, z["rot"], qo, kc, vc, table, c.tok_slot, c.tok_pos, rows, H, G,
+                                                 dk, dk, True, err))
+        out["prepare_" + label]["without_norm"] = bytes_point(us, moved)
+        del projs
+        # -- the router: sigmoid scores with a correction beside a softmax over all outputs with one -------------------------
+        E, top = z["experts"], z["top"]
+        zl = torch.randn(rows, E, device=dev)
+        ids = torch.zeros(rows, top, dtype=torch.int32, device=dev)
+        rank = torch.zeros_like(ids)
+        wts = torch.zeros(rows, top, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        corr = torch.zeros(E, device=dev)
+        us0 = timed(lambda i: counts.zero_())
+        us = timed(lambda i: (counts.zero_(), ops.moe_route_scored(zl, E, top, 1, 1, 0, 1.0, corr, None, ids, wts, rank, counts, rows, scoring="sigmoid")))
+        out["router_" + label] = {"suposun": {"us": round(us - us0, 1)}}
+        us = timed(lambda i: (counts.zero_(), ops.moe_route_scored(zl, E, top, 1, 1, 0, 1.0, corr, None, ids, wts, rank, counts, rows)))
+        out["router_" + label]["softmax_all"] = {"us": round(us - us0, 1)}
+        # -- the experts' gate: bounded beside x·sigmoid(x) ------------------------------------------------------------------
+        ff, P = z["expert_ff"], rows * top
+        n_u = max(2, int(300e6 // (P * 2 * ff * 2)) + 1)
+        us_ = [torch.randn(P, 2 * ff, device=dev).to(bf) for _ in range(n_u)]
+        a = torch.zeros(P, ff, dtype=bf, device=dev)
+        us = timed(lambda i: ops.gate_mul_clamped(us_[i % n_u][:, :ff], us_[i % n_u][:, ff:], a, 7.0, 1.702, P, ff))
+        out["expert_gate_" + label] = {"suposun": bytes_point(us, P * ff * 6)}
+        us = timed(lambda i: ops.gate_mul(us_[i % n_u][:, :ff], us_[i % n_u][:, ff:], a, "silu", P, ff))
+        out["expert_gate_" + label]["silu"] = bytes_point(us, P * ff * 6)
+        del us_
+        # -- the dense feed-forward's gate on float32 products: tanh GELU beside relu ------------------------------------------
+        ffg = z["ff_gated"]
+        n_g = max(2, int(300e6 // (rows * 2 * ffg * 4)) + 1)
+        gus = [torch.randn(rows, 2 * ffg, device=dev) for _ in range(n_g)]
+        u = torch.zeros(rows, ffg, dtype=bf, device=dev)
+        us = timed(lambda i: ops.gate_mul(gus[i % n_g][:, :ffg], gus[i % n_g][:, ffg:], u, "gelu_tanh", rows, ffg))
+        out["dense_gate_" + label] = {"suposun": bytes_point(us, rows * ffg * 10)}
+        us = timed(lambda i: ops.gate_mul(gus[i % n_g][:, :ffg], gus[i % n_g][:, ffg:], u, "relu", rows, ffg))
+        out["dense_gate_" + label]["relu"] = bytes_point(us, rows * ffg * 10)
+        del gus
+        # -- the embedding with its bigram row beside a scaled embedding -------------------------------------------------------
+        V, buckets = z["vocab"], z["buckets"]
+        table_e, pairs_t = torch.randn(V, width, device=dev).to(bf), torch.randn(buckets + 1, width, device=dev).to(bf)
+        kept = torch.zeros(max(S, B), 2, dtype=torch.int32, device=dev)
+        toks = [torch.randint(0, V, (rows,), dtype=torch.int32, device=dev) for _ in range(4)]
+        x = torch.zeros(rows, width, device=dev)
+
+        def emb(i):
+            c.tokens = toks[i % 4]
+            ops.embed_bigram(table_e, pairs_t, buckets, 1000003, 31, 1.0, kept, c, x)
+        us = timed(emb)
+        out["embed_" + label] = {"suposun": bytes_point(us, rows * width * 8)}
+        us = timed(lambda i: ops.embed_streams(table_e, toks[i % 4], x, 1, 2.0, err))
+        out["embed_" + label]["scaled"] = bytes_point(us, rows * width * 6)
+        del table_e, pairs_t
+    return out
+
+
 def design_bench(args) -> int:
     """`--design NAME`: the design at sizes like a real model's layers (random weights) beside its closest existing
     model of equal size (GPT-2; for Rakelorn, Kuvusun): prefill and decode throughput, and each kernel's time.  One JSON line."""
@@ -864,8 +1040,9 @@ def design_bench(args) -> int:
             "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": {}}
     sizes, config_of, kernels_of = {"kuvusun": (DESIGN_SIZES, kuvusun_config, design_kernels),
                                     "kotisun": (KOTISUN_SIZES, kotisun_config, kotisun_kernels),
-                                    "rakelorn": (RAKELORN_SIZES, rakelorn_config, rakelorn_kernels)}[args.design]
-    beside, beside_of = ("kuvusun", kuvusun_config_like) if args.design == "rakelorn" else ("gpt2", gpt2_config_like)
+                                    "rakelorn": (RAKELORN_SIZES, rakelorn_config, rakelorn_kernels),
+                                    "suposun": (SUPOSUN_SIZES, suposun_config, suposun_kernels)}[args.design]
+    beside, beside_of = {"rakelorn": ("kuvusun", kuvusun_config_like), "suposun": ("kuvusun", kuvusun_config)}.get(args.design, ("gpt2", gpt2_config_like))
     line["beside"] = beside
     for name in args.design_sizes.split(","):
         z = sizes[name]
@@ -926,9 +1103,9 @@ def main() -> int:
                     help="with --only decode or prefill and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
-    ap.add_argument("--design", default=None, choices=["kuvusun", "kotisun", "rakelorn"],
+    ap.add_argument("--design", default=None, choices=["kuvusun", "kotisun", "rakelorn", "suposun"],
                     help="instead of the default workload: this design at sizes like a real model's layers beside its closest "
-                         "existing model of equal size (GPT-2; for rakelorn, Kuvusun)")
+                         "existing model of equal size (GPT-2; for rakelorn and suposun, Kuvusun)")
     ap.add_argument("--design-sizes", default="s,m", help="with --design: which of the sizes %s" % ",".join(DESIGN_SIZES))
     ap.add_argument("--design-no-kernels", action="store_true", help="with --design: whole steps only, not each kernel alone")
     ap.add_argument("--design-only-kernels", action="store_true", help="with --design: each kernel alone only")

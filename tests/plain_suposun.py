@@ -20,7 +20,7 @@ def rms_norm(x, w, eps):
 
 
 def one_plus_rms_norm(x, w, eps):
-    """The same with a weight stored around zero: the factor is 1 + w."""
+    """The same where w holds the offset from one: the factor is 1 + w."""
     return rms_norm(x, 1.0 + w, eps)
 
 
@@ -116,7 +116,8 @@ def attend(q, k, v, scale, mask=None, softcap=None, sink=None):
 
 def attention(h, w, p, m, eps, positions):
     """Mixer "attention": values are the projected keys themselves; query/key norm per head with one weight for all
-    heads; interleaved rotation; capped scores; window with kept first tokens; sinks; a sigmoid gate per head."""
+    heads; rotation of neighbouring pairs; a cap on the scores; a window beside which the leading tokens stay visible;
+    sinks; a sigmoid gate per head."""
     T, H, G, n = h.shape[0], m["heads"], m["kv_heads"], m["dim"]
     q = (h @ w[p + "q"].T).view(T, H, n)
     k = (h @ w[p + "k"].T).view(T, G, n)

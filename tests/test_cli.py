@@ -138,3 +138,25 @@ def test_run_generates_with_a_rakelorn_model_what_the_plain_implementation_would
                    "--dtype", "float32"], capsys)
     outputs = [line for prev, line in zip(out.splitlines(), out.splitlines()[1:]) if prev.startswith("--- Output")]
     assert [[int(t) for t in line.split()] for line in outputs] == [plain_rakelorn.greedy_generate(cfg, w, p, 6) for p in ([5, 17, 3, 400, 44], [7])]
+
+
+def test_init_and_info_take_a_suposun_preset(tmp_path, capsys):
+    run_cli(["init", "--config", "suposun-tiny", "--out", str(tmp_path / "s"), "--seed", "3"], capsys)
+    info = run_cli(["info", "--model", str(tmp_path / "s")], capsys)
+    assert "architecture: Suposun" in info
+    shown = json.loads(info[info.index("{"):info.rindex("}") + 1])
+    assert shown["embedding"]["bigram"]["buckets"] == 251 and [layer["type"] for layer in shown["layers"]] == [
+        "attention_2", "attention", "attention_2", "attention"] and shown["layers"][2]["mixer"]["kv_from"] == 0
+
+
+@pytest.mark.gpu
+def test_run_generates_with_a_suposun_model_what_the_plain_implementation_would(tmp_path, capsys):
+    import plain_suposun
+    run_cli(["init", "--config", "suposun-tiny", "--out", str(tmp_path / "s"), "--seed", "3"], capsys)
+    cfg, w = plain_suposun.read_model_dir(tmp_path / "s")
+    f = tmp_path / "prompts.txt"
+    f.write_text("5 17 3 400 44\n7\n")
+    out = run_cli(["run", "--model", str(tmp_path / "s"), "--prompts-file", str(f), "--tokens", "6", "--greedy", "--stop-id", "999",
+                   "--dtype", "float32"], capsys)
+    outputs = [line for prev, line in zip(out.splitlines(), out.splitlines()[1:]) if prev.startswith("--- Output")]
+    assert [[int(t) for t in line.split()] for line in outputs] == [plain_suposun.greedy_generate(cfg, w, p, 6) for p in ([5, 17, 3, 400, 44], [7])]

@@ -125,7 +125,7 @@ class _KVGroup:
             first = max(0, cur_len + 1 - self.need.window) // BLOCK_TOKENS  # oldest key the first query sees
         last = (new_len + BLOCK_TOKENS - 1) // BLOCK_TOKENS
         row = self.table_host[slot]
-        # (the blocks of the kept first tokens are taken while the sequence passes them and never given back)
+        # (the blocks of the leading tokens that stay visible are taken while the sequence passes them and never given back)
         return [i for i in range(first, last) if row[i] < 0]
 
     def kept_blocks(self) -> int:
@@ -177,7 +177,7 @@ class SequenceCache:
                 if need.kind == "window" and need.window <= 0:
                     raise CacheError("a window need has a positive window")
                 if getattr(need, "keep_first", 0) < 0 or (getattr(need, "keep_first", 0) and need.kind != "window"):
-                    raise CacheError("kept first tokens belong to a window need and are not negative")
+                    raise CacheError("keep_first belongs to a window need and is not negative")
                 g = _KVGroup(need, entries, self.n_blocks, self.n_slots, self.max_blocks, dtype, self.device)
             elif isinstance(need, StateNeed):
                 g = _StateGroup(need, entries, self.n_slots, self.device)

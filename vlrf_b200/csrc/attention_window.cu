@@ -22,7 +22,7 @@
 //   sums several branches puts a branch's weight there) and written at a column offset of wider rows.
 //   Further parameters (attn_window_ex): softcap c > 0 squashes every score to c · tanh(score / c) after the scale;
 //   keep_first n > 0 lets every query also see the keys at positions below n, whatever the window (they keep their
-//   positions); sink (one float32 a query head) adds exp(sink_h) to the softmax's denominator, with no key and no value.
+//   positions); sink (one float32 a query head) adds the term exp(sink_h) to the softmax's denominator and nothing to its numerator.
 #include "common.cuh"
 
 namespace {

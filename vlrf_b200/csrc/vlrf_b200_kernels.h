@@ -263,7 +263,7 @@ int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const vo
                      float scale, int window, float out_scale, int* dev_err, cudaStream_t stream);
 // The same with a cap on the scores (softcap > 0: score ← softcap · tanh(score / softcap), after the scale), keys at
 // positions below keep_first visible whatever the window, and sink (null, or a float32 per query head): exp(sink[h])
-// is added to the softmax's denominator, with no key and no value.
+// is one more term of the softmax's denominator, with nothing in the numerator.
 int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                         const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
                         float scale, int window, float out_scale, float softcap, int keep_first, const float* sink, int* dev_err,

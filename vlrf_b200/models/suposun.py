@@ -70,10 +70,11 @@ def weight_spec(cfg: SuposunConfig) -> list[TensorSpec]:
 
 
 def random_weights(cfg: SuposunConfig, gen: torch.Generator) -> dict:
-    """Matrices N(0, 1/in); the norms on sublayer outputs and the model's norm (stored around zero) N(0, 0.1); the norms of
-    queries and keys 1 + N(0, 0.1); layer scales 0.5 + N(0, 0.1); sinks N(0, 1); the routers' corrections N(0, 0.05); the
-    embedding N(0, 1) (its scale and the bigram table, N(0, 1) too, make a first residual of the layers' size): no term
-    of a formula is hidden by a zero or a one."""
+    """Matrices N(0, 1/in); the norms on sublayer outputs and the model's norm (whose stored weights are offsets from one) N(0, 0.1); the norms of
+    queries and keys 1 + N(0, 0.1); layer scales 0.5 + N(0, 0.1); sinks N(0, 1); the routers' corrections N(0, 0.05): no
+    term of a formula is hidden by a zero or a one.  The embedding is drawn so that a scaled row has a size of 0.06, and
+    the bigram table N(0, 0.3): with the embedding as head a token's own embedding otherwise dominates its logits, and
+    a random model does nothing but repeat its last token whatever its layers compute."""
     out = {}
     for spec in weight_spec(cfg):
         if spec.optional:
@@ -90,8 +91,10 @@ def random_weights(cfg: SuposunConfig, gen: torch.Generator) -> dict:
             t = 1.0 + 0.1 * t
         elif spec.kind == "vector":
             t = 0.1 * t
-        elif name in ("embed", "bigram"):
-            pass
+        elif name == "embed":
+            t = t * (0.06 / max(abs(cfg.embedding_scale), 1e-6))
+        elif name == "bigram":
+            t = 0.3 * t
         else:
             t = t / float(spec.shape[-1]) ** 0.5
         out[name] = t

@@ -36,7 +36,7 @@ class GroupRMSNorm:
     float32.  `accumulate=True` adds the result to the (float32) output rows instead of replacing them, which is
     what a block needs that norms a sublayer's output before the residual sum.
 
-    `offset` is added to the stored weight (1.0 for weights that are stored around zero, y = x̂ · (1 + w)), and
+    `offset` is added to the stored weight (1.0 where a checkpoint holds the offset from one, y = x̂ · (1 + w)), and
     `post_scale`, a vector, multiplies the normed row element by element (a layer scale on a sublayer's normed output);
     both are folded into one float32 factor per column when the part is made."""
 

@@ -19,7 +19,7 @@ What else is a parameter, each absent by default:
   rotary                   its pairing (halves or neighbours), its frequency table and its factor on cosines and sines
   softcap c                score ← c · tanh(score / c) after the scale
   keep_first n             with a window: keys at positions below n stay visible to every later query
-  sink [heads]             exp(sink_h) is added to the softmax's denominator of head h: it has no key and no value
+  sink [heads]             one more term exp(sink_h) in the denominator of head h's softmax, with nothing in the numerator
   w_gate [heads, width]    head h's result is multiplied by sigmoid(w_gate_h · input) ahead of the output projection; the
                            gate's logits ride in the input product as `heads` more float32 columns
 
@@ -62,7 +62,7 @@ class WindowAttention:
         if window < 0:
             raise ValueError("window attention: a window is positive, or 0 for none")
         if keep_first < 0 or (keep_first > 0 and window <= 0):
-            raise ValueError("window attention: kept first tokens go with a window and are not negative")
+            raise ValueError("window attention: keep_first goes with a window and is not negative")
         if softcap is not None and not softcap > 0.0:
             raise ValueError(f"window attention: a cap of {softcap} on the scores is not positive")
         if qk_norm not in (None, "head", "all"):
