@@ -142,9 +142,10 @@ def attention_case(H, G, dk, window, keep, softcap, sinks, dtype, lens, seed):
     return q, k, v, sink, torch.cat(want)
 
 
-def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, splits=None):
+def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, splits=None, gate=None):
     """Everything is appended to a NaN-filled cache under a permuted block table; then the last `tail` tokens of every
-    sequence (None: all of them, by the kernel that takes a warp per token and head) attend."""
+    sequence (None: all of them, by the kernel that takes a warp per token and head) attend.  gate: float32 [T, H] logits of
+    a gate per head, handed over as a range of columns of wider rows."""
     from vlrf_b200.csrc import ops
     from vlrf_b200.parts.context import Workspace
     T, H, dk = q.shape
@@ -159,9 +160,17 @@ def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, split
     ops.qkv_rope_append(proj, 0, H * dk, H * dk + G * dk, None, 0, qo, cache.k, cache.v, cache.table, tok_slot, tok_pos, T, H, G, dk, dk, True, err)
     sk = dev(sink) if sink is not None else None
     extra = dict(softcap=softcap or 0.0, keep_first=keep, sink=sk)
+
+    def gate_rows(rows):
+        if gate is None:
+            return None
+        wide = torch.full((len(rows), H + 5), float("nan"))
+        wide[:, 2:2 + H] = gate[torch.tensor(rows)].float()
+        return dev(wide)[:, 2:2 + H]
     if tail is None:
         out = torch.full((T, H * dk), float("nan"), dtype=dtype, device=DEV)
-        ops.attention_window(qo, cache.k, cache.v, cache.table, tok_slot, tok_pos, out, T, H, G, dk, dk, 0.5, window, 1.0, err, **extra)
+        ops.attention_window(qo, cache.k, cache.v, cache.table, tok_slot, tok_pos, out, T, H, G, dk, dk, 0.5, window, 1.0, err,
+                             gate=gate_rows(list(range(T))), **extra)
         rows = list(range(T))
     else:
         rows, seq_start, seq_pos0, start = [], [0], [], 0
@@ -181,7 +190,8 @@ def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, split
         if splits:
             os.environ["VLRF_B200_DECODE_SPLITS"] = str(splits)
         try:
-            ops.attention_window_step(qo[idx.to(DEV)].contiguous(), cache.k, cache.v, cache.table, out, ctx, H, G, dk, dk, 0.5, window, 1.0, **extra)
+            ops.attention_window_step(qo[idx.to(DEV)].contiguous(), cache.k, cache.v, cache.table, out, ctx, H, G, dk, dk, 0.5, window, 1.0,
+                                      gate=gate_rows(rows), **extra)
         finally:
             os.environ.pop("VLRF_B200_DECODE_SPLITS", None)
     assert int(err.item()) == 0
@@ -195,13 +205,18 @@ def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, split
     (2, 2, 128, 65, 63, 12.0, True)])
 def test_attention_at_the_edges(H, G, dk, window, keep, softcap, sinks, dtype, tol):
     """Sequences of 1, 2, 64, 65, 129, 200 and 333 tokens in one step: as one prompt step (both kernels), as a later portion
-    of 70 and of 3 tokens, and as a decode step whose contexts are whole, cut in 2 and cut in 5 parts."""
+    of 70 and of 3 tokens, and as a decode step whose contexts are whole, cut in 2 and cut in 5 parts.  Where the shape has
+    sinks it also has a gate per head, applied by the attention kernels themselves."""
     lens = [1, 2, 64, 65, 129, 200, 333]
     q, k, v, sink, want = attention_case(H, G, dk, window, keep, softcap, sinks, dtype, lens, dk * 7 + window)
-    got, rows = run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, None)
+    gate = None
+    if sinks:
+        gate = torch.randn(sum(lens), H, generator=torch.Generator().manual_seed(dk)).double() * 2.0
+        want = want * torch.sigmoid(gate.float().double())[:, :, None]
+    got, rows = run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, None, gate=gate)
     close(got, want, tol, "a warp per token and head")
     for tail, splits in ((10 ** 6, None), (70, None), (3, None), (1, 1), (1, 2), (1, 5)):
-        got, rows = run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, splits)
+        got, rows = run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, splits, gate=gate)
         close(got, want[torch.tensor(rows)], tol, f"the last {tail} tokens, contexts in {splits} parts")
 
 

@@ -110,12 +110,12 @@ _SIGNATURES = {
                                   _c_int, _c_void_p, _c_void_p, _c_float, _c_int, _c_float, _c_void_p, _c_void_p],
     "vlrf_attn_window_ex": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float, _c_float, _c_int, _c_void_p,
-                            _c_void_p, _c_void_p],
+                            _c_void_p, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_window_mma_ex": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                 _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float,
-                                _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p],
+                                _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "vlrf_embed_bigram": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
-                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_scale_values": [_c_void_p, ctypes.c_longlong, _c_float, _c_void_p],
     "vlrf_gate_mul_clamped": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                               _c_float, _c_void_p],

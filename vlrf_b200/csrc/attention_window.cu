@@ -22,7 +22,8 @@
 //   sums several branches puts a branch's weight there) and written at a column offset of wider rows.
 //   Further parameters (attn_window_ex): softcap c > 0 squashes every score to c · tanh(score / c) after the scale;
 //   keep_first n > 0 lets every query also see the keys at positions below n, whatever the window (they keep their
-//   positions); sink (one float32 a query head) adds the term exp(sink_h) to the softmax's denominator and nothing to its numerator.
+//   positions); gate (float32 [T][ld_gate], a logit per query head) multiplies head h's result by sigmoid(gate[t][h]);
+//   sink (one float32 a query head) adds the term exp(sink_h) to the softmax's denominator and nothing to its numerator.
 #include "common.cuh"
 
 namespace {
@@ -56,7 +57,10 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
         cs_sm[half + i] = sn * magnitude;
     }
     const int n_kh = write_cache ? Hkv : 0;
-    if (norm == 1) {
+    // Heads normed by themselves, of an even size up to 256: a warp takes a head whole (below), with its entries in registers
+    const bool warp_heads = norm == 1 && (dk & 1) == 0 && dk <= 256;
+    if (warp_heads) {
+    } else if (norm == 1) {
         for (int h = warp; h < H + n_kh; h += 4) {
             const float* head = h < H ? row + q_off + h * dk : row + k_off + (h - H) * dk;
             float ss = 0.f;
@@ -100,10 +104,88 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
         if (c < half) return x * cs_sm[c] - normed(head, w, inv, c + half) * cs_sm[half + c];
         return x * cs_sm[c - half] + normed(head, w, inv, c - half) * cs_sm[c];
     };
-    for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
-        const int h = i / dk, c = i - h * dk;
-        const float* w = norm == 2 ? q_norm + h * dk : q_norm;
-        ElemIO<ET>::store(q_out + (size_t)t * ldq + i, rotated(row + q_off + h * dk, w, norm ? inv_sm[h] : 1.f, c));
+    if (warp_heads) {
+        // A warp per head, queries and keys alike: a lane holds up to four pairs of entries (the two of a rotation, or two
+        // neighbours behind the rotated ones), the head's sum of squares is a sum over the warp, and norm, rotation and
+        // store follow from the registers: every entry is read once and no warp waits for another.
+        const int hd2 = dk / 2;
+        int blk = -1;
+        if (write_cache) {
+            const int bi = pos / BT;
+            blk = (pos >= 0 && bi < max_blocks) ? block_table[(size_t)slot * max_blocks + bi] : -1;
+            if (blk < 0 && threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+        }
+        const int n_all = H + (blk >= 0 ? Hkv : 0);
+        for (int h = warp; h < n_all; h += 4) {
+            const bool isq = h < H;
+            const float* head = isq ? row + q_off + h * dk : row + k_off + (h - H) * dk;
+            const float* w = isq ? q_norm : k_norm;
+            ET* dst = isq ? q_out + (size_t)t * ldq + h * dk : Kc + (((size_t)blk * Hkv + (h - H)) * BT + (pos % BT)) * dk;
+            float xa[4], xb[4];
+            int ia[4], ib[4];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int u = lane + 32 * j;
+                xa[j] = xb[j] = 0.f;
+                ia[j] = ib[j] = 0;
+                if (u < hd2) {
+                    const bool turns = u < half;
+                    ia[j] = turns ? (pairing == 1 ? 2 * u : u) : rot + 2 * (u - half);
+                    ib[j] = turns ? (pairing == 1 ? 2 * u + 1 : u + half) : ia[j] + 1;
+                    xa[j] = head[ia[j]];
+                    xb[j] = head[ib[j]];
+                    ss = fmaf(xa[j], xa[j], fmaf(xb[j], xb[j], ss));
+                }
+            }
+            ss = warp_sum(ss);
+            const float inv = 1.f / sqrtf(ss / (float)dk + eps);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int u = lane + 32 * j;
+                if (u < hd2) {
+                    const float na = xa[j] * inv * w[ia[j]], nb = xb[j] * inv * w[ib[j]];
+                    const bool turns = u < half;
+                    ElemIO<ET>::store(dst + ia[j], turns ? na * cs_sm[u] - nb * cs_sm[half + u] : na);
+                    ElemIO<ET>::store(dst + ib[j], turns ? nb * cs_sm[u] + na * cs_sm[half + u] : nb);
+                }
+            }
+        }
+        if (blk < 0) return;
+        for (int i = threadIdx.x; i < Hkv * dv; i += blockDim.x) {
+            const int h = i / dv, c = i - h * dv;
+            ElemIO<ET>::store(Vc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dv + c, row[v_off + i]);
+        }
+        return;
+    }
+    // Heads of an even size: a thread takes a pair of entries at a time, the two of a rotation (entries 2u and 2u + 1, or u
+    // and u + rot/2) or two neighbours behind the rotated ones, so every entry is read and normed once.
+    const int hd = dk / 2;
+    auto pair_of = [&](const float* head, const float* w, float inv, int u, int& ia, int& ib, float& oa, float& ob) {
+        const bool turns = u < half;
+        ia = turns ? (pairing == 1 ? 2 * u : u) : rot + 2 * (u - half);
+        ib = turns ? (pairing == 1 ? 2 * u + 1 : u + half) : ia + 1;
+        const float xa = normed(head, w, inv, ia), xb = normed(head, w, inv, ib);
+        oa = turns ? xa * cs_sm[u] - xb * cs_sm[half + u] : xa;
+        ob = turns ? xb * cs_sm[u] + xa * cs_sm[half + u] : xb;
+    };
+    const bool by_pairs = (dk & 1) == 0;
+    if (by_pairs) {
+        for (int i = threadIdx.x; i < H * hd; i += blockDim.x) {
+            const int h = i / hd, u = i - h * hd;
+            int ia, ib;
+            float oa, ob;
+            pair_of(row + q_off + h * dk, norm == 2 ? q_norm + h * dk : q_norm, norm ? inv_sm[h] : 1.f, u, ia, ib, oa, ob);
+            ET* dst = q_out + (size_t)t * ldq + h * dk;
+            ElemIO<ET>::store(dst + ia, oa);
+            ElemIO<ET>::store(dst + ib, ob);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
+            const int h = i / dk, c = i - h * dk;
+            const float* w = norm == 2 ? q_norm + h * dk : q_norm;
+            ElemIO<ET>::store(q_out + (size_t)t * ldq + i, rotated(row + q_off + h * dk, w, norm ? inv_sm[h] : 1.f, c));
+        }
     }
     if (!write_cache) return;
     const int bi = pos / BT;
@@ -112,11 +194,23 @@ qkv_rope_append_kernel(const float* __restrict__ proj, int ld, int q_off, int k_
         if (threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
         return;
     }
-    for (int i = threadIdx.x; i < Hkv * dk; i += blockDim.x) {
-        const int h = i / dk, c = i - h * dk;
-        const float* w = norm == 2 ? k_norm + h * dk : k_norm;
-        ElemIO<ET>::store(Kc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dk + c,
-                          rotated(row + k_off + h * dk, w, norm ? inv_sm[H + h] : 1.f, c));
+    if (by_pairs) {
+        for (int i = threadIdx.x; i < Hkv * hd; i += blockDim.x) {
+            const int h = i / hd, u = i - h * hd;
+            int ia, ib;
+            float oa, ob;
+            pair_of(row + k_off + h * dk, norm == 2 ? k_norm + h * dk : k_norm, norm ? inv_sm[H + h] : 1.f, u, ia, ib, oa, ob);
+            ET* dst = Kc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dk;
+            ElemIO<ET>::store(dst + ia, oa);
+            ElemIO<ET>::store(dst + ib, ob);
+        }
+    } else {
+        for (int i = threadIdx.x; i < Hkv * dk; i += blockDim.x) {
+            const int h = i / dk, c = i - h * dk;
+            const float* w = norm == 2 ? k_norm + h * dk : k_norm;
+            ElemIO<ET>::store(Kc + (((size_t)blk * Hkv + h) * BT + (pos % BT)) * dk + c,
+                              rotated(row + k_off + h * dk, w, norm ? inv_sm[H + h] : 1.f, c));
+        }
     }
     for (int i = threadIdx.x; i < Hkv * dv; i += blockDim.x) {
         const int h = i / dv, c = i - h * dv;
@@ -130,7 +224,7 @@ attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ 
                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tok_slot,
                    const int* __restrict__ tok_pos, ET* __restrict__ out, int ld_out, int H, int Hkv, int dk, int dv, int BT,
                    float scale, int window, float out_scale, float softcap, int keep_first, const float* __restrict__ sink,
-                   int* __restrict__ dev_err) {
+                   const float* __restrict__ gate, int ld_gate, int* __restrict__ dev_err) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float q_sm[];  // [AW_WARPS][dk]
@@ -199,7 +293,8 @@ attn_window_kernel(const ET* __restrict__ q_in, int ldq, const ET* __restrict__ 
 #pragma unroll
         for (int i = 0; i < AW_MAX / 32; ++i) acc[i] *= corr;
     }
-    const float inv = (l > 0.f) ? out_scale / l : 0.f;
+    float inv = (l > 0.f) ? out_scale / l : 0.f;
+    if (gate != nullptr) inv *= sigmoid_f(gate[(size_t)t * ld_gate + h]);      // a gate per head on the head's result
     ET* dst = out + (size_t)t * ld_out + (size_t)h * dv;
 #pragma unroll
     for (int i = 0; i < AW_MAX / 32; ++i) {
@@ -253,13 +348,14 @@ extern "C" int vlrf_qkv_rope_append(const float* proj, int ld, int q_off, int k_
 extern "C" int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table,
                                    int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H,
                                    int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale, float softcap,
-                                   int keep_first, const float* sink, int* dev_err, cudaStream_t stream) {
+                                   int keep_first, const float* sink, const float* gate, int ld_gate, int* dev_err,
+                                   cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && H > 0 && Hkv > 0 && max_blocks > 0, "attn_window: bad sizes");
     VLRF_REQUIRE(H % Hkv == 0, "attn_window: %d heads cannot share %d key/value heads", H, Hkv);
     VLRF_REQUIRE(dk > 0 && dk <= AW_MAX && dv > 0 && dv <= AW_MAX, "attn_window: head sizes %d and %d are not in 1…%d", dk, dv, AW_MAX);
     VLRF_REQUIRE(BT % 32 == 0, "attn_window: cache blocks of %d tokens are not a multiple of 32", BT);
     VLRF_REQUIRE(window >= 0 && keep_first >= 0 && softcap >= 0.f, "attn_window: negative window, kept tokens or cap");
-    VLRF_REQUIRE(ldq >= H * dk && ld_out >= H * dv, "attn_window: leading sizes are smaller than the rows");
+    VLRF_REQUIRE(ldq >= H * dk && ld_out >= H * dv && (gate == nullptr || ld_gate >= H), "attn_window: leading sizes are smaller than the rows");
     VLRF_REQUIRE(dev_err != nullptr, "attn_window: needs the device error word");
     if (T == 0) return VLRF_OK;
     dim3 grid(T, (H + AW_WARPS - 1) / AW_WARPS);
@@ -267,11 +363,12 @@ extern "C" int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void
     if (dtype == VLRF_F32)
         launch_chained(attn_window_kernel<float>, grid, dim3(AW_WARPS * 32), smem, stream, (const float*)q, ldq, (const float*)Kc,
                        (const float*)Vc, block_table, max_blocks, tok_slot, tok_pos, (float*)out, ld_out, H, Hkv, dk, dv, BT, scale,
-                       window, out_scale, softcap, keep_first, sink, dev_err);
+                       window, out_scale, softcap, keep_first, sink, gate, ld_gate, dev_err);
     else if (dtype == VLRF_BF16)
         launch_chained(attn_window_kernel<__nv_bfloat16>, grid, dim3(AW_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq,
                        (const __nv_bfloat16*)Kc, (const __nv_bfloat16*)Vc, block_table, max_blocks, tok_slot, tok_pos,
-                       (__nv_bfloat16*)out, ld_out, H, Hkv, dk, dv, BT, scale, window, out_scale, softcap, keep_first, sink, dev_err);
+                       (__nv_bfloat16*)out, ld_out, H, Hkv, dk, dv, BT, scale, window, out_scale, softcap, keep_first, sink, gate, ld_gate,
+                       dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "attn_window: unknown dtype %d", dtype);
     return vlrf_check_launch("attn_window");
@@ -282,5 +379,5 @@ extern "C" int vlrf_attn_window(const void* q, int dtype, int ldq, const void* K
                                 int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale, int* dev_err,
                                 cudaStream_t stream) {
     return vlrf_attn_window_ex(q, dtype, ldq, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out, T, H, Hkv, dk, dv, BT,
-                               scale, window, out_scale, 0.f, 0, nullptr, dev_err, stream);
+                               scale, window, out_scale, 0.f, 0, nullptr, nullptr, 0, dev_err, stream);
 }

@@ -17,7 +17,8 @@
 // Parameters beside the window: softcap c > 0 squashes every scaled score to c · tanh(score / c); keep_first n > 0 lets
 // every query also see the keys at positions below n (the tiles that hold them come first in a CTA's list of tiles,
 // ahead of the window's); sink (a float32 per query head) adds exp(sink_h) to the softmax's denominator where the parts
-// of a row are complete (in the kernel, or in the merge of a cut context).
+// of a row are complete (in the kernel, or in the merge of a cut context); gate (float32 [rows][ld_gate], a logit per
+// query head) multiplies head h's finished result by sigmoid(gate[row][h]), at the same places.
 #include "common.cuh"
 
 namespace {
@@ -60,7 +61,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                        __nv_bfloat16* __restrict__ out, int ld_out, float* __restrict__ partials, int H, int Hkv, int dk, int dv,
                        float scale, int window, float out_scale, int n_split, float softcap, int keep_first,
-                       const float* __restrict__ sink, int* __restrict__ dev_err) {
+                       const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate, int* __restrict__ dev_err) {
     constexpr int KS = DKP + 8, VS = DVP + 8;       // row strides in elements: 16 bytes of padding keep ldmatrix off bank conflicts
     constexpr int WKEYS = DEC ? WM_BK / WM_WARPS : WM_BK;      // keys of a tile that one warp takes
     constexpr int NT_S = WKEYS / 8, NT_O = DVP / 8, KS_QK = DKP / 16, KS_PV = WKEYS / 16;
@@ -263,7 +264,8 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                     L = L * f + exp2f(sk - M2);
                     acc *= f;
                 }
-                if (c < dv) out[(size_t)row * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * (out_scale / L) : 0.f);
+                const float gf = gate != nullptr ? sigmoid_f(gate[(size_t)row * ld_gate + h]) : 1.f;
+                if (c < dv) out[(size_t)row * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * (gf * out_scale / L) : 0.f);
             } else {
                 float* dst = partials + (((size_t)row * H + h) * n_split + part) * (dv + 2);
                 if (c < dv) dst[c] = acc;
@@ -285,6 +287,7 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
                 fo = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - M2);
                 l_run[r] = l_run[r] * fo + exp2f(sk - M2);
             }
+            if (gate != nullptr) fo *= sigmoid_f(gate[(size_t)row * ld_gate + h]);
             const float inv = (l_run[r] > 0.f) ? fo * out_scale / l_run[r] : 0.f;
             __nv_bfloat16* dst = out + (size_t)row * ld_out + (size_t)h * dv + 2 * t;
 #pragma unroll
@@ -304,7 +307,8 @@ attn_window_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_
 // order of the parts.  A part that saw no key has l = 0.
 __global__ void __launch_bounds__(128)
 attn_window_merge_kernel(const float* __restrict__ partials, const int* __restrict__ seq_slot, __nv_bfloat16* __restrict__ out,
-                         int ld_out, int H, int dv, int n_split, float out_scale, const float* __restrict__ sink) {
+                         int ld_out, int H, int dv, int n_split, float out_scale, const float* __restrict__ sink,
+                         const float* __restrict__ gate, int ld_gate) {
     pdl_wait();
     pdl_launch_dependents();
     const int row = blockIdx.x, h = blockIdx.y;
@@ -320,7 +324,7 @@ attn_window_merge_kernel(const float* __restrict__ partials, const int* __restri
         const float l = p[s * (dv + 2) + dv + 1];
         if (l > 0.f) L += l * exp2f(p[s * (dv + 2) + dv] - M);
     }
-    const float inv = L > 0.f ? out_scale / L : 0.f;
+    const float inv = (L > 0.f ? out_scale / L : 0.f) * (gate != nullptr ? sigmoid_f(gate[(size_t)row * ld_gate + h]) : 1.f);
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < n_split; ++s)
@@ -333,7 +337,7 @@ template <int DKP, int DVP, bool DEC>
 int launch_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                       const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                       int n_seqs, int max_new, int H, int Hkv, int dk, int dv, float scale, int window, float out_scale, int n_split,
-                      float softcap, int keep_first, const float* sink, int* dev_err, cudaStream_t stream) {
+                      float softcap, int keep_first, const float* sink, const float* gate, int ld_gate, int* dev_err, cudaStream_t stream) {
     // stages of a decode step: as many as leave room for two or three CTAs an SM
     constexpr int NST = DEC ? (DKP + DVP <= 160 ? 4 : DKP + DVP <= 224 ? 3 : 2) : 2;
     const size_t smem = (size_t)((DEC ? 16 : 64) * (DKP + 8) + NST * 64 * (DKP + 8) + NST * 64 * (DVP + 8)) * 2;
@@ -349,7 +353,7 @@ int launch_window_mma(const void* q, int ldq, const void* Kc, const void* Vc, co
     cudaError_t e = launch_chained(kern, grid, dim3(WM_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)Kc,
                                    (const __nv_bfloat16*)Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0,
                                    (__nv_bfloat16*)out, ld_out, partials, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap,
-                                   keep_first, sink, dev_err);
+                                   keep_first, sink, gate, ld_gate, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_window_mma: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_window_mma");
 }
@@ -366,11 +370,11 @@ extern "C" int vlrf_attn_window_mma_ex(const void* q, int ldq, const void* Kc, c
                                        const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out,
                                        float* partials, int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale,
                                        int window, float out_scale, int n_split, float softcap, int keep_first, const float* sink,
-                                       int* dev_err, cudaStream_t stream) {
+                                       const float* gate, int ld_gate, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_attn_window_mma_takes(H, Hkv, dk, dv, BT, ldq, ld_out), "attn_window_mma: heads %d/%d, sizes %d and %d, block %d are not taken",
                  H, Hkv, dk, dv, BT);
     VLRF_REQUIRE(n_seqs >= 0 && max_new >= 0 && max_blocks > 0 && window >= 0 && dev_err != nullptr, "attn_window_mma: bad arguments");
-    VLRF_REQUIRE(keep_first >= 0 && softcap >= 0.f, "attn_window_mma: negative kept tokens or cap");
+    VLRF_REQUIRE(keep_first >= 0 && softcap >= 0.f && (gate == nullptr || ld_gate >= H), "attn_window_mma: negative kept tokens or cap, or gate rows shorter than the heads");
     VLRF_REQUIRE(n_seqs <= 65535 && Hkv <= 65535, "attn_window_mma: too many sequences or heads for one launch");
     VLRF_REQUIRE(n_split >= 1 && (n_split == 1 || (max_new == 1 && partials != nullptr)),
                  "attn_window_mma: contexts are cut into parts in decode steps only, and the parts need scratch");
@@ -380,16 +384,16 @@ extern "C" int vlrf_attn_window_mma_ex(const void* q, int ldq, const void* Kc, c
     int st = VLRF_ERR_UNSUPPORTED;
     const bool dec = max_new == 1 && H / Hkv <= 16;            // every tile holds one token's heads: the warps deal the keys
 #define GO(A, B) if (kp == A && vp == B) st = dec ? launch_window_mma<A, B, true>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
-        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, dev_err, stream) \
+        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, gate, ld_gate, dev_err, stream) \
         : launch_window_mma<A, B, false>(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, \
-        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, dev_err, stream);
+        out, ld_out, partials, n_seqs, max_new, H, Hkv, dk, dv, scale, window, out_scale, n_split, softcap, keep_first, sink, gate, ld_gate, dev_err, stream);
     GO(32, 32) GO(32, 64) GO(32, 96) GO(32, 128) GO(64, 32) GO(64, 64) GO(64, 96) GO(64, 128)
     GO(96, 32) GO(96, 64) GO(96, 96) GO(96, 128) GO(128, 32) GO(128, 64) GO(128, 96) GO(128, 128)
 #undef GO
     if (st != VLRF_OK) return st;
     if (n_split > 1) {
         launch_chained(attn_window_merge_kernel, dim3(n_seqs, H), dim3(128), (size_t)0, stream, (const float*)partials, seq_slot,
-                       (__nv_bfloat16*)out, ld_out, H, dv, n_split, out_scale, sink);
+                       (__nv_bfloat16*)out, ld_out, H, dv, n_split, out_scale, sink, gate, ld_gate);
         return vlrf_check_launch("attn_window_merge");
     }
     return VLRF_OK;
@@ -400,6 +404,6 @@ extern "C" int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, cons
                                     float* partials, int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale,
                                     int window, float out_scale, int n_split, int* dev_err, cudaStream_t stream) {
     return vlrf_attn_window_mma_ex(q, ldq, Kc, Vc, block_table, max_blocks, seq_slot, seq_start, seq_pos0, out, ld_out, partials,
-                                   n_seqs, max_new, H, Hkv, dk, dv, BT, scale, window, out_scale, n_split, 0.f, 0, nullptr, dev_err,
-                                   stream);
+                                   n_seqs, max_new, H, Hkv, dk, dv, BT, scale, window, out_scale, n_split, 0.f, 0, nullptr, nullptr, 0,
+                                   dev_err, stream);
 }

@@ -958,18 +958,22 @@ def softcap(values, n_rows: int, cap: float) -> None:
     call("vlrf_softcap", _ptr(values), n_rows * values.shape[1], float(cap), _stream())
 
 
-def embed_bigram(table, pairs, buckets: int, mul_prev: int, mul_cur: int, scale: float, kept, ctx, out) -> None:
+def embed_bigram(table, pairs, buckets: int, mul_prev: int, mul_cur: int, scale: float, kept, ctx, out, also=None) -> None:
     """out[t] = table[token] · scale + pairs[(token before · mul_prev + token · mul_cur) mod buckets] (pairs[buckets] for a
     sequence's first token): float32 [T, d].  kept: int32 [slots, 2], every sequence's last token by the parity of its
-    length (see the kernel library's header)."""
+    length (see the kernel library's header).  also: a bfloat16 tensor [T, d] that receives the rows' rounding as well."""
     _dev(table, "table"); _dev(pairs, "pairs", table.dtype); _dev(kept, "kept", torch.int32); _dev(out, "out", torch.float32)
+    if also is not None:
+        _dev(also, "also", torch.bfloat16)
+        if also.shape[0] < ctx.n_tokens or also.shape[1] != table.shape[1]:
+            raise KernelError("embed_bigram: the second output does not match")
     V, d = table.shape
     if tuple(pairs.shape) != (buckets + 1, d) or out.shape[0] < ctx.n_tokens or out.shape[1] != d or kept.dim() != 2 \
             or kept.shape[1] != 2 or not kept.is_contiguous():
         raise KernelError("embed_bigram: sizes do not match")
     call("vlrf_embed_bigram", _ptr(table), _ptr(pairs), dtype_code(table.dtype), _ptr(ctx.tokens), _ptr(ctx.tok_slot), _ptr(ctx.tok_pos),
          _ptr(ctx.seq_start), ctx.n_seqs, _ptr(kept), _ptr(out), ctx.n_tokens, d, V, int(buckets), int(mul_prev), int(mul_cur),
-         float(scale), _ptr(ctx.dev_err), _stream())
+         float(scale), _ptr(also), _ptr(ctx.dev_err), _stream())
 
 
 def scale_values(values, n_rows: int, factor: float) -> None:
@@ -1029,12 +1033,21 @@ def qkv_rope_append(proj, q_off: int, k_off: int, v_off: int, freq, rot: int, q_
          1 if interleaved else 0, float(magnitude), _ptr(dev_err), _stream())
 
 
+def _check_head_gate(gate, n_rows: int, n_heads: int) -> None:
+    if gate is not None:
+        _rows(gate, "gate", torch.float32)
+        if gate.shape[0] < n_rows or gate.shape[1] < n_heads:
+            raise KernelError("attention_window: the gate has one float32 logit per token and query head")
+
+
 def attention_window(q, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n_tokens: int, n_heads: int, n_kv_heads: int,
                      dk: int, dv: int, scale: float, window: int, out_scale: float, dev_err, *, softcap: float = 0.0,
-                     keep_first: int = 0, sink=None) -> None:
+                     keep_first: int = 0, sink=None, gate=None) -> None:
     """Each token's queries attend the visible keys of its slot; out may be a range of columns of wider rows.  softcap > 0
     squashes the scaled scores; keys at positions below keep_first stay visible whatever the window; sink: float32
-    [heads], exp(sink) joins the softmax's denominator."""
+    [heads], exp(sink) joins the softmax's denominator; gate: float32 [T, ≥ heads] (a range of columns of wider rows will
+    do), head h's result times sigmoid(gate[t, h])."""
+    _check_head_gate(gate, n_tokens, n_heads)
     if sink is not None:
         _dev(sink, "sink", torch.float32)
         if sink.numel() != n_heads:
@@ -1048,7 +1061,8 @@ def attention_window(q, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n
         raise KernelError("attention_window: output does not match")
     call("vlrf_attn_window_ex", _ptr(q), dtype_code(q.dtype), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
          block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.stride(0), n_tokens, n_heads, n_kv_heads, dk, dv, bt,
-         float(scale), int(window), float(out_scale), float(softcap), int(keep_first), _ptr(sink), _ptr(dev_err), _stream())
+         float(scale), int(window), float(out_scale), float(softcap), int(keep_first), _ptr(sink), _ptr(gate),
+         gate.stride(0) if gate is not None else 0, _ptr(dev_err), _stream())
 
 
 # ---- a state-space recurrence with a matrix state per head -----------------------------------------------------------------
@@ -1126,7 +1140,7 @@ def window_decode_splits(n_rows: int, n_kv_heads: int, max_context: int, window:
 
 
 def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, scale: float,
-                          window: int, out_scale: float, *, softcap: float = 0.0, keep_first: int = 0, sink=None) -> None:
+                          window: int, out_scale: float, *, softcap: float = 0.0, keep_first: int = 0, sink=None, gate=None) -> None:
     """The attention of a step (prompt tokens, single tokens or a mix) with the kernel that suits it: bfloat16 sizes that
     the tensor-core kernel takes go there (a decode step's contexts cut into parts), everything else to the kernel
     that takes a warp per token and head."""
@@ -1143,13 +1157,14 @@ def attention_window_step(q, k_cache, v_cache, block_table, out, ctx, n_heads: i
             _dev(sink, "sink", torch.float32)
             if sink.numel() != n_heads:
                 raise KernelError("attention_window: one sink per query head")
+        _check_head_gate(gate, ctx.n_tokens, n_heads)
         call("vlrf_attn_window_mma_ex", _ptr(q), q.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(out), out.stride(0), _ptr(partials), ctx.n_seqs,
              ctx.max_new, n_heads, n_kv_heads, dk, dv, bt, float(scale), int(window), float(out_scale), n_split, float(softcap),
-             int(keep_first), _ptr(sink), _ptr(ctx.dev_err), _stream())
+             int(keep_first), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(ctx.dev_err), _stream())
         return
     attention_window(q, k_cache, v_cache, block_table, ctx.tok_slot, ctx.tok_pos, out, ctx.n_tokens, n_heads, n_kv_heads, dk, dv,
-                     scale, window, out_scale, ctx.dev_err, softcap=softcap, keep_first=keep_first, sink=sink)
+                     scale, window, out_scale, ctx.dev_err, softcap=softcap, keep_first=keep_first, sink=sink, gate=gate)
 
 
 def ssd_scan_step(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, ctx, y, n_heads: int, n_groups: int, n_state: int, p: int) -> None:

@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(ST_THREADS)
 embed_bigram_kernel(const WT* __restrict__ table, const WT* __restrict__ pairs, const int* __restrict__ tokens,
                     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ seq_start, int n_seqs,
                     int* __restrict__ kept, float* __restrict__ x, int T, int d, int V, int buckets, int mul_prev, int mul_cur,
-                    float scale, int* __restrict__ dev_err) {
+                    float scale, __nv_bfloat16* __restrict__ also, int* __restrict__ dev_err) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int row_sm;
@@ -86,7 +86,11 @@ embed_bigram_kernel(const WT* __restrict__ table, const WT* __restrict__ pairs, 
     const WT* er = table + (size_t)id * d;
     const WT* br = pairs + (size_t)row_sm * d;
     float* out = x + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += ST_THREADS) out[i] = fmaf(ElemIO<WT>::load(er + i), scale, ElemIO<WT>::load(br + i));
+    for (int i = threadIdx.x; i < d; i += ST_THREADS) {
+        const float v = fmaf(ElemIO<WT>::load(er + i), scale, ElemIO<WT>::load(br + i));
+        out[i] = v;
+        if (also != nullptr) also[(size_t)t * d + i] = __float2bfloat16_rn(v);     // what the first sublayer reads of the row
+    }
 }
 
 __global__ void scale_values_kernel(float* __restrict__ v, long long n, float factor) {
@@ -284,17 +288,18 @@ extern "C" int vlrf_streams_write_read(float* x, const float* mix, const float* 
 
 extern "C" int vlrf_embed_bigram(const void* table, const void* pairs, int w_dtype, const int* tokens, const int* tok_slot,
                                  const int* tok_pos, const int* seq_start, int n_seqs, int* kept, float* x, int T, int d, int V,
-                                 int buckets, int mul_prev, int mul_cur, float scale, int* dev_err, cudaStream_t stream) {
+                                 int buckets, int mul_prev, int mul_cur, float scale, void* also, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && d > 0 && V > 0 && buckets > 0 && n_seqs >= 0, "embed_bigram: bad sizes");
     VLRF_REQUIRE(dev_err != nullptr && kept != nullptr && seq_start != nullptr, "embed_bigram: needs the error word, the kept tokens and the sequences' rows");
     if (T == 0 || n_seqs == 0) return VLRF_OK;
     if (w_dtype == VLRF_F32)
         launch_chained(embed_bigram_kernel<float>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, (const float*)table, (const float*)pairs,
-                       tokens, tok_slot, tok_pos, seq_start, n_seqs, kept, x, T, d, V, buckets, mul_prev, mul_cur, scale, dev_err);
+                       tokens, tok_slot, tok_pos, seq_start, n_seqs, kept, x, T, d, V, buckets, mul_prev, mul_cur, scale, (__nv_bfloat16*)also,
+                       dev_err);
     else if (w_dtype == VLRF_BF16)
         launch_chained(embed_bigram_kernel<__nv_bfloat16>, dim3(T), dim3(ST_THREADS), (size_t)0, stream, (const __nv_bfloat16*)table,
                        (const __nv_bfloat16*)pairs, tokens, tok_slot, tok_pos, seq_start, n_seqs, kept, x, T, d, V, buckets, mul_prev,
-                       mul_cur, scale, dev_err);
+                       mul_cur, scale, (__nv_bfloat16*)also, dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "embed_bigram: unknown dtype %d", w_dtype);
     return vlrf_check_launch("embed_bigram");

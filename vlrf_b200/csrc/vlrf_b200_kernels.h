@@ -233,9 +233,10 @@ int vlrf_scale_values(float* v, long long n, float factor, cudaStream_t stream);
 // (token before · mul_prev + token · mul_cur) mod buckets, or `buckets` at position 0.  The token before is the row above
 // where tok_slot and tok_pos say so, else kept[slot][position & 1]; kept int32 [slots][2] receives every sequence's last
 // token of the step at the parity of the position behind it (seq_start: n_seqs + 1 first rows of the sequences' tokens).
+// also: null, or bfloat16 [T][d] that receives the rounding of every written row (padding rows are left alone).
 int vlrf_embed_bigram(const void* table, const void* pairs, int w_dtype, const int* tokens, const int* tok_slot, const int* tok_pos,
                       const int* seq_start, int n_seqs, int* kept, float* x, int T, int d, int V, int buckets, int mul_prev,
-                      int mul_cur, float scale, int* dev_err, cudaStream_t stream);
+                      int mul_cur, float scale, void* also, int* dev_err, cudaStream_t stream);
 
 // ---- attention with key and value sizes of their own (attention_window.cu) -------------------------------------------------
 // From the float32 rows of a layer's input product (queries at q_off: H·dk columns, keys at k_off: Hkv·dk, values at
@@ -263,11 +264,12 @@ int vlrf_attn_window(const void* q, int dtype, int ldq, const void* Kc, const vo
                      float scale, int window, float out_scale, int* dev_err, cudaStream_t stream);
 // The same with a cap on the scores (softcap > 0: score ← softcap · tanh(score / softcap), after the scale), keys at
 // positions below keep_first visible whatever the window, and sink (null, or a float32 per query head): exp(sink[h])
-// is one more term of the softmax's denominator, with nothing in the numerator.
+// is one more term of the softmax's denominator, with nothing in the numerator.  gate (null, or float32 [T][ld_gate], a logit
+// per query head): head h's result is multiplied by sigmoid(gate[t][h]).
 int vlrf_attn_window_ex(const void* q, int dtype, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                         const int* tok_slot, const int* tok_pos, void* out, int ld_out, int T, int H, int Hkv, int dk, int dv, int BT,
-                        float scale, int window, float out_scale, float softcap, int keep_first, const float* sink, int* dev_err,
-                        cudaStream_t stream);
+                        float scale, int window, float out_scale, float softcap, int keep_first, const float* sink, const float* gate,
+                        int ld_gate, int* dev_err, cudaStream_t stream);
 
 // The same attention on the tensor cores (attention_window_mma.cu; bfloat16): a CTA per key/value head, sequence and tile
 // of 64 (token, query head) rows, for prompt steps (rows seq_start[i] … of q are sequence i's new tokens, the first at
@@ -278,11 +280,12 @@ int vlrf_attn_window_mma(const void* q, int ldq, const void* Kc, const void* Vc,
                          const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                          int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale,
                          int n_split, int* dev_err, cudaStream_t stream);
-// … with the cap, the kept first keys and the sinks of vlrf_attn_window_ex.
+// … with the cap, the kept first keys, the sinks and the gate per head of vlrf_attn_window_ex.
 int vlrf_attn_window_mma_ex(const void* q, int ldq, const void* Kc, const void* Vc, const int* block_table, int max_blocks,
                             const int* seq_slot, const int* seq_start, const int* seq_pos0, void* out, int ld_out, float* partials,
                             int n_seqs, int max_new, int H, int Hkv, int dk, int dv, int BT, float scale, int window, float out_scale,
-                            int n_split, float softcap, int keep_first, const float* sink, int* dev_err, cudaStream_t stream);
+                            int n_split, float softcap, int keep_first, const float* sink, const float* gate, int ld_gate, int* dev_err,
+                            cudaStream_t stream);
 
 // ---- a state-space recurrence with a matrix state per head (ssd.cu) ----------------------------------------------------------
 // What a sequence keeps lies in `state`, float32 [slots][2][state_row]: per copy the heads' states [H][N][P] and, at

@@ -27,7 +27,9 @@ class TokenEmbedding:
                 raise ValueError("TokenEmbedding: the bigram table is [buckets + 1, width] in the embedding's dtype")
             if norm is not None or streams != 1 or getattr(position, "where", None) == "embedding":
                 raise ValueError("TokenEmbedding: a bigram table goes with one stream, no norm and no position table")
-            self.bigram = (table, int(table.shape[0]) - 1, int(mul_prev), int(mul_cur))
+            buckets = int(table.shape[0]) - 1
+            # (a multiplier enters the hash only through its remainder, which keeps every product inside 64 bits)
+            self.bigram = (table, buckets, int(mul_prev) % buckets, int(mul_cur) % buckets)
         self.norm = norm
         self.vocab_size, self.width = weight.shape
         self.scale, self.streams = float(scale), int(streams)
@@ -72,7 +74,12 @@ class TokenEmbedding:
                 raise ValueError("TokenEmbedding: a bigram table needs the sequences' kept tokens")
             table, buckets, mul_prev, mul_cur = self.bigram
             ctx.ws.row_stats.forget()
-            ops.embed_bigram(self.weight, table, buckets, mul_prev, mul_cur, self.scale, state, ctx, x)
+            # In the bfloat16 engine the kernel also leaves the rows' rounding where a block that reads the residual itself
+            # looks for it (`Workspace.input_cast`), which spares the first layer a cast kernel.
+            also = ctx.ws.get("block_input", ctx.n_tokens, x.shape[1], ctx.act_dtype) if ctx.act_dtype == torch.bfloat16 else None
+            ops.embed_bigram(self.weight, table, buckets, mul_prev, mul_cur, self.scale, state, ctx, x, also=also)
+            if also is not None:
+                ctx.ws.input_cast = (x.data_ptr(), ctx.n_tokens, id(ctx))
             return x
         if self.scale != 1.0 or self.streams != 1:
             ctx.ws.row_stats.forget()

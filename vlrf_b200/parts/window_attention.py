@@ -126,9 +126,10 @@ class WindowAttention:
                             interleaved=bool(getattr(self.rotary, "interleaved", False)),
                             magnitude=float(getattr(self.rotary, "magnitude", 1.0)))
         ops.attention_window_step(q, view.k, view.v, view.block_table, merged, ctx, H, G, self.dim, self.vdim, self.scale,
-                                  self.window, factor, softcap=self.softcap, keep_first=self.keep_first, sink=self.sink)
-        if self.gate_off is not None:        # head h times sigmoid of its gate logit (a float32 column of the input product)
-            ops.gate_mul(proj[:, self.gate_off:self.gate_off + H], merged, merged, "sigmoid", T, H * self.vdim, per=self.vdim)
+                                  self.window, factor, softcap=self.softcap, keep_first=self.keep_first, sink=self.sink,
+                                  # head h times sigmoid of its gate logit (a float32 column of the input product), applied by
+                                  # the attention kernel where it writes the head's result
+                                  gate=proj[:, self.gate_off:self.gate_off + H] if self.gate_off is not None else None)
 
     def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, accumulate: bool = True) -> None:
         T = ctx.n_tokens
