@@ -872,7 +872,7 @@ def suposun_config(z: dict) -> dict:
         m.update(more)
         return {"type": kind, "mixer": m}
     win = att("attention", softcap=30.0, mask={"size": z["window"], "keep_first": z["keep"]})
-    win["mixer"]["rot"] = {"base": 1e6, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    win["mixer"]["rot"] = {"base": 1e6, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
     layers = [dict(att("attention_2"), mlp={"kind": "dense", "ff": z["ff_gated"]}), dict(win, mlp=moe),
               dict(att("attention_2", kv_from=0), mlp=moe), dict(win, mlp=moe)]

@@ -60,7 +60,7 @@ SUP_B = {"architecture": "Suposun", "vocab": 257, "width": 128, "norm": {"eps": 
 #: sizes that are no multiples of 8 (the attention kernels of the CUDA cores); one bucket; a multiplier of zero; a window of 7
 SUP_ODD = {"architecture": "Suposun", "vocab": 199, "width": 100, "norm": {"eps": 1e-5}, "logit_scale": 1.5,
            "embedding": {"scale": 0.5, "bigram": {"buckets": 1, "mul_prev": 0, "mul_cur": 3}}, "layers": [
-    layer(att(5, 1, 12, 0.28, 6, base=3000.0, scaling=(2.0, 32, 4.0, 1.0), softcap=5.0, mask=(7, 3)), moe(28, 1.5, 7, 3)),
+    layer(att(5, 1, 12, 0.28, 6, base=3000.0, scaling=(2.0, 32, 4.0, 1.0), softcap=5.0, mask=(7, 3)), moe(28, 1.4, 7, 3)),
     layer(att2(2, 1, 20, 28, 0.22, 10, base=700.0), dense(44)),
     layer(att(3, 3, 12, 0.3, 12, mask=(130, 1)), moe(36, 0.6, 2, 1)),
 ]}

@@ -201,7 +201,7 @@ def run_attention(q, k, v, sink, lens, window, keep, softcap, dtype, tail, split
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("H,G,dk,window,keep,softcap,sinks", [
     (4, 1, 16, 40, 5, 6.0, True), (6, 2, 32, 70, 0, 10.0, True), (4, 4, 8, 64, 64, None, True), (8, 2, 8, 33, 70, 30.0, True),
-    (5, 1, 12, 7, 3, 4.0, True), (3, 3, 64, 130, 1, None, False), (2, 1, 24, 0, 0, 9.0, True), (16, 1, 64, 100, 20, 20.0, False),
+    (5, 1, 12, 7, 3, 4.0, True), (3, 3, 64, 130, 1, None, False), (2, 1, 24, 0, 0, 9.0, True), (16, 1, 64, 100, 24, 18.0, False),
     (2, 2, 128, 65, 63, 12.0, True)])
 def test_attention_at_the_edges(H, G, dk, window, keep, softcap, sinks, dtype, tol):
     """Sequences of 1, 2, 64, 65, 129, 200 and 333 tokens in one step: as one prompt step (both kernels), as a later portion
@@ -293,7 +293,7 @@ def test_bigram_embedding_over_steps(V, d, buckets, mul_prev, mul_cur, dtype):
     assert all(int(kept[s, 0]) == 1 << 30 for s in (1, 2, 4, 6))
 
 
-@pytest.mark.parametrize("E,top", [(5, 2), (12, 4), (3, 3), (7, 1), (40, 6), (130, 8)])
+@pytest.mark.parametrize("E,top", [(5, 2), (11, 4), (3, 3), (7, 1), (40, 6), (130, 8)])
 def test_router_by_sigmoid_scores(E, top):
     from vlrf_b200.csrc import ops
     g = torch.Generator().manual_seed(E)

@@ -25,8 +25,8 @@ def draw_mlp(r: random.Random):
     if x < 0.12:
         return None
     if x < 0.5:
-        return dense(r.choice([24, 40, 64, 100, 136, 320]))
-    experts = r.choice([1, 2, 3, 4, 6, 12, 17, 40])
+        return dense(r.choice([24, 40, 64, 100, 136, 304]))
+    experts = r.choice([1, 2, 3, 4, 6, 11, 17, 40])
     return moe(r.choice([24, 40, 64, 96, 136]), r.choice([0.5, 1.0, 1.5, 3.0, 7.0]), experts, r.randint(1, min(experts, 6)))
 
 
@@ -42,8 +42,8 @@ def draw_config(seed: int) -> dict:
         if r.random() < 0.85:
             cfg["embedding"]["scale"] = r.choice([0.7, 1.0, 2.5, 8.0, 16.0])
         if r.random() < 0.8:
-            cfg["embedding"]["bigram"] = {"buckets": r.choice([1, 7, 64, 509, 4099]), "mul_prev": r.choice([0, 1, 127, 100003]),
-                                          "mul_cur": r.choice([0, 1, 7, 31])}
+            cfg["embedding"]["bigram"] = {"buckets": r.choice([1, 7, 64, 521, 4099]), "mul_prev": r.choice([0, 1, 131, 100003]),
+                                          "mul_cur": r.choice([0, 1, 5, 31])}
     n_layers = r.choice([1, 2, 3, 4, 5, 6])
     kinds = r.choice(["mixed", "mixed", "mixed", "attention", "attention_2"])
     layers, owners = [], {}
@@ -54,12 +54,12 @@ def draw_config(seed: int) -> dict:
             kv = r.choice([1, 1, 2, 3, 4])
             heads = kv * r.choice([1, 2, 4, 6])
             rot = r.choice([d for d in (2, 4, 6, 8, 16, 32, 64, 128) if d <= dim])
-            scaling = (r.choice([2.0, 8.0, 32.0]), r.choice([16, 64, 512]), r.choice([4.0, 32.0]), r.choice([0.5, 1.0, 2.0])) if r.random() < 0.7 else None
+            scaling = (r.choice([2.0, 8.0, 32.0]), r.choice([16, 64, 1024]), r.choice([4.0, 24.0]), r.choice([0.5, 1.0, 2.0])) if r.random() < 0.7 else None
             mask = None
             if r.random() < 0.85:
-                mask = (r.choice([1, 5, 31, 64, 65, 100, 128, 136, 200]), r.choice([None, 0, 1, 20, 64, 70, 150]))
+                mask = (r.choice([1, 5, 31, 64, 65, 100, 128, 140, 200]), r.choice([None, 0, 1, 24, 64, 70, 150]))
             mixer = att(heads, kv, dim, round(dim ** -0.5 * r.choice([0.8, 1.0, 1.4]), 4), rot, base=r.choice([100.0, 10000.0, 1e6]),
-                        scaling=scaling, softcap=r.choice([None, 5.0, 20.0, 50.0]), mask=mask)
+                        scaling=scaling, softcap=r.choice([None, 5.0, 18.0, 50.0]), mask=mask)
         else:
             if owners and r.random() < 0.45:
                 j = r.choice(list(owners))
