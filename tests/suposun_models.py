@@ -78,9 +78,11 @@ SHARP_FACTOR = 5.0
 MODELS = {"sup_a": SUP_A, "sup_b": SUP_B, "sup_odd": SUP_ODD, "sup_sharp": SUP_SHARP}
 
 
-def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0) -> None:
+def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0, correction: float = 10.0) -> None:
     """The package's random draw for the configuration, the matrices that make queries multiplied by `sharp`, and the
-    routers' corrections drawn ten times wider (fewer close calls between experts, see the plain `decided_prefix`)."""
+    routers' corrections drawn `correction` times wider: ten times leaves fewer close calls between experts (see the
+    plain `decided_prefix`) while the scores still take part in the choice; a hundred times lets the corrections decide
+    alone, so that no choice rests on rounding and bfloat16 can be compared at every position."""
     import vlrf_b200.models  # noqa: F401
     from vlrf_b200.registry import parse_config
     from vlrf_b200.weights import write_safetensors
@@ -90,7 +92,7 @@ def write_model(cfg: dict, seed: int, out_dir, sharp: float = 1.0) -> None:
         if name.endswith("mix.q"):
             tensors[name] = tensors[name] * sharp
         if name.endswith("mlp.correction"):
-            tensors[name] = tensors[name] * 10.0
+            tensors[name] = tensors[name] * correction
     Path(out_dir).mkdir(parents=True, exist_ok=True)
     (Path(out_dir) / "config.json").write_text(json.dumps(cfg, indent=2))
     write_safetensors(Path(out_dir) / "model.safetensors",
